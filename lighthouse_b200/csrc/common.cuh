@@ -1,0 +1,152 @@
+// Shared host-side definitions for the library's translation units: the
+// context object, error reporting, dtype helpers and the internal kernel
+// launch entry points each .cu file provides.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/lh_b200.h"
+
+struct lh_ctx {
+  int device = 0;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;  // the stream launches go to (own or external)
+  int* dev_status = nullptr;      // device word kernels write a DeviceError into
+  int* host_status = nullptr;     // pinned mirror read by lh_b200_sync
+  int64_t launches = 0;
+  char err[512] = {0};
+  // tensor-map encoder resolved from the driver at context creation
+  void* encode_tiled = nullptr;
+  // scratch for split/partial results and for L2 flushing in benchmarks
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  // NCCL
+  void* nccl_lib = nullptr;
+  void* nccl_comm = nullptr;
+  int rank = 0, world = 1;
+};
+
+namespace lh {
+
+int set_error(lh_ctx* ctx, int code, const char* fmt, ...);
+char* global_error_buffer();
+
+#define LH_CUDA_CHECK(ctx, expr)                                                                   \
+  do {                                                                                             \
+    cudaError_t e__ = (expr);                                                                      \
+    if (e__ != cudaSuccess)                                                                        \
+      return lh::set_error((ctx), LH_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), \
+                           __FILE__, __LINE__);                                                    \
+  } while (0)
+
+#define LH_CHECK_LAUNCH(ctx, name)                                                                 \
+  do {                                                                                             \
+    cudaError_t e__ = cudaGetLastError();                                                          \
+    if (e__ != cudaSuccess)                                                                        \
+      return lh::set_error((ctx), LH_ERR_CUDA, "launch of %s failed: %s", (name), cudaGetErrorString(e__)); \
+    (ctx)->launches++;                                                                             \
+  } while (0)
+
+inline size_t dtype_size(int dt) {
+  switch (dt) {
+    case LH_F32: return 4;
+    case LH_BF16: return 2;
+    case LH_F16: return 2;
+    case LH_I32: return 4;
+    case LH_I64: return 8;
+    case LH_F64: return 8;
+  }
+  return 0;
+}
+
+inline char* data_ptr(const lh_memref_t* m) {
+  return static_cast<char*>(m->aligned) + m->offset * (int64_t)dtype_size(m->dtype);
+}
+
+inline bool is_contiguous(const lh_memref_t* m) {
+  int64_t expect = 1;
+  for (int i = m->rank - 1; i >= 0; --i) {
+    if (m->shape[i] != 1 && m->strides[i] != expect) return false;
+    expect *= m->shape[i];
+  }
+  return true;
+}
+
+inline int64_t numel(const lh_memref_t* m) {
+  int64_t n = 1;
+  for (int i = 0; i < m->rank; ++i) n *= m->shape[i];
+  return n;
+}
+
+// ------------------------------------------------------------- GEMM problem
+// One (possibly batched) product with its epilogue, in element strides.
+struct GemmProblem {
+  int M, N, K, batch;
+  const void* A; int a_dtype; int64_t sam, sak, sab;  // A(m,k) at A + m*sam + k*sak (+ b*sab)
+  const void* B; int b_dtype; int64_t sbk, sbn, sbb;  // B(k,n)
+  void* D; int d_dtype; int64_t sdm, sdn, sdb;
+  const void* C; int c_dtype; int64_t scm, scn, scb;      // added before bias/act (may be null)
+  const void* bias; int bias_dtype;                        // [N] (may be null)
+  const void* R; int r_dtype; int64_t srm, srn, srb;      // added after act (may be null)
+  int act;
+  uint32_t flags;
+};
+
+// Epilogue parameters passed by value to the kernels.
+struct EpiParams {
+  void* D; int d_dtype; int64_t ldd;
+  const void* C; int c_dtype; int64_t ldc;
+  const void* bias; int bias_dtype;
+  const void* R; int r_dtype; int64_t ldr;
+  int act;
+  int swiglu;
+};
+
+int gemm_tc_bf16_supported(const lh_ctx* ctx, const GemmProblem& p);
+int gemm_tc_bf16_launch(lh_ctx* ctx, const GemmProblem& p);
+int gemm_tc_tf32x3_supported(const lh_ctx* ctx, const GemmProblem& p);
+int gemm_tc_tf32x3_launch(lh_ctx* ctx, const GemmProblem& p);
+int gemm_simt_launch(lh_ctx* ctx, const GemmProblem& p);
+
+// -------------------------------------------------------- attention problem
+struct AttnProblem {
+  int B, Hq, Hkv, Sq, Skv, D;
+  int dtype;  // Q/K/V/O element type
+  const void* Q; int64_t sqb, sqh, sqs;  // unit stride in D
+  const void* K; int64_t skb, skh, sks;
+  const void* V; int64_t svb, svh, svs;
+  void* O; int64_t sob, soh, sos;
+  int o_dtype;
+  float scale;
+  int causal;
+};
+int attn_tc_supported(const lh_ctx* ctx, const AttnProblem& p);
+int attn_tc_launch(lh_ctx* ctx, const AttnProblem& p);
+int attn_simt_launch(lh_ctx* ctx, const AttnProblem& p);
+
+// ------------------------------------------------------------ row operators
+int layernorm_launch(lh_ctx* ctx, const lh_memref_t* out, const lh_memref_t* x, const lh_memref_t* gamma,
+                     const lh_memref_t* beta, float eps, int rms);
+int softmax_launch(lh_ctx* ctx, const lh_memref_t* out, const lh_memref_t* x);
+int rope_launch(lh_ctx* ctx, const lh_memref_t* x, float theta, int pos0);
+int elementwise_launch(lh_ctx* ctx, int kind, const lh_memref_t* out, const lh_memref_t* a,
+                       const lh_memref_t* b, int act, float scalar);
+int embedding_launch(lh_ctx* ctx, const lh_memref_t* out, const lh_memref_t* ids, const lh_memref_t* wte,
+                     const lh_memref_t* wpe, int period);
+
+// Encodes a tiled tensor map through the driver entry point the context resolved.
+// dims/strides are innermost-first; strides_bytes[0] is implied by the element size.
+int encode_tensor_map(lh_ctx* ctx, CUtensorMap* out, int dtype, int rank, void* base, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box, int swizzle128);
+
+int ensure_scratch(lh_ctx* ctx, size_t bytes);
+
+}  // namespace lh
