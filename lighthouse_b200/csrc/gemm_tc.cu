@@ -6,8 +6,11 @@
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) into one
 //               of two f32 accumulators in tensor memory, so the epilogue of tile t
 //               overlaps the main loop of tile t+1
-//   warps 2-5   epilogue: tcgen05.ld the accumulator (one row per thread), add
-//               C / bias, activation, residual, round, 16-byte global stores
+//   warps 2-5   epilogue: each warp owns 32 accumulator rows; per 64 columns it reads
+//               them with tcgen05.ld, adds C / bias, applies the activation, adds the
+//               residual, rounds, writes a 32-row x 128-byte block into its own
+//               swizzled staging buffer and hands it to a TMA store (coalesced,
+//               clipped at the matrix edge, asynchronous)
 // Hand-offs are mbarriers; every wait is bounded (ptx.cuh) and a wait that runs out
 // raises a status word instead of hanging.
 //
@@ -27,9 +30,12 @@ constexpr int BK = 64;                      // 64 bf16 = one 128-byte swizzle ro
 constexpr int A_TILE_BYTES = BM * BK * 2;   // 16 KiB
 constexpr int NUM_THREADS = 192;
 constexpr int GROUP_M = 16;                 // tile rasterisation: 16 row-blocks share B column-blocks in L2
+constexpr int STAGING_BUF_BYTES = 32 * 128; // 32 rows x 128 bytes
+constexpr int STAGING_BYTES = 4 * 2 * STAGING_BUF_BYTES;  // 4 epilogue warps x 2 buffers
 
 struct GemmTcParams {
   int M, N, K;
+  int n_out;  // columns of D (N, or N/2 with the SwiGLU epilogue)
   int num_m_blocks, num_n_blocks, num_k_blocks;
   EpiParams epi;
   int* dev_status;
@@ -43,10 +49,12 @@ template <int BN, int STAGES>
 struct SmemLayout {
   static constexpr int B_TILE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int STAGING_OFFSET = STAGES * STAGE_BYTES;  // multiple of 1024
+  static constexpr int BAR_OFFSET = STAGING_OFFSET + STAGING_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for the 1024-byte alignment of the ring
+  static_assert(DYN_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA can opt into");
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
@@ -74,10 +82,82 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, v
   return ok != 0;
 }
 
-template <int BN, bool B_KMAJOR, int STAGES>
+// 16-byte chunk j of this lane's 128-byte row in a 32-row staging buffer laid out with
+// the 128-byte swizzle the output tensor map expects (chunk index XOR row mod 8).
+__device__ __forceinline__ void stage_chunk(uint8_t* buf, int lane, int j, uint4 val) {
+  *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = val;
+}
+
+// Activation over a register block; the switch is outside the loop so that only the
+// selected activation's code is ever fetched.
+template <int N_>
+__device__ __forceinline__ void activate_block(float (&v)[N_], int act) {
+  switch (act) {
+    case LH_ACT_NONE: break;
+    case LH_ACT_RELU:
+#pragma unroll
+      for (int i = 0; i < N_; ++i) v[i] = fmaxf(v[i], 0.f);
+      break;
+    case LH_ACT_GELU_ERF:
+#pragma unroll
+      for (int i = 0; i < N_; ++i) v[i] = apply_act(v[i], LH_ACT_GELU_ERF);
+      break;
+    case LH_ACT_GELU_TANH:
+#pragma unroll
+      for (int i = 0; i < N_; ++i) v[i] = apply_act(v[i], LH_ACT_GELU_TANH);
+      break;
+    case LH_ACT_SILU:
+#pragma unroll
+      for (int i = 0; i < N_; ++i) v[i] = apply_act(v[i], LH_ACT_SILU);
+      break;
+    default:
+#pragma unroll
+      for (int i = 0; i < N_; ++i) v[i] = apply_act(v[i], LH_ACT_SIGMOID);
+      break;
+  }
+}
+
+// Adds the 128 bytes of a C / residual row segment held in eight 16-byte registers.
+template <bool F32, int N_>
+__device__ __forceinline__ void add_row_segment(float (&v)[N_], const uint4 (&seg)[8]) {
+  if (F32) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[j * 4 + 0] += __uint_as_float(seg[j].x);
+      v[j * 4 + 1] += __uint_as_float(seg[j].y);
+      v[j * 4 + 2] += __uint_as_float(seg[j].z);
+      v[j * 4 + 3] += __uint_as_float(seg[j].w);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&seg[j]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(h[q]);
+        v[j * 8 + q * 2] += f.x;
+        v[j * 8 + q * 2 + 1] += f.y;
+      }
+    }
+  }
+}
+
+// Loads this lane's 128-byte row segment (8 x 16 bytes) starting at element `elem0`;
+// vectors past column `n_out` are skipped (n_out is a multiple of 8).
+template <bool F32>
+__device__ __forceinline__ void load_row_segment(uint4 (&seg)[8], const void* base, int64_t elem0, int col0, int n_out) {
+  constexpr int EPV = F32 ? 4 : 8;
+  const char* ptr = static_cast<const char*>(base) + elem0 * (F32 ? 4 : 2);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    seg[j] = (col0 + j * EPV < n_out) ? __ldg(reinterpret_cast<const uint4*>(ptr) + j) : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmTcParams p) {
+                    const __grid_constant__ CUtensorMap tmD, const GemmTcParams p) {
   using L = SmemLayout<BN, STAGES>;
   constexpr int TMEM_COLS = tmem_cols_for(BN);
   extern __shared__ uint8_t smem_raw[];
@@ -107,6 +187,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmD);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -191,6 +272,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, +32) belong to this warp
     const EpiParams& e = p.epi;
+    uint8_t* stage_bufs = smem + L::STAGING_OFFSET + quarter * (2 * STAGING_BUF_BYTES);
+    int sbuf = 0;
     int t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       int m_blk, n_blk;
@@ -200,81 +283,98 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (!mbar_wait_warp(&tmem_full[buf], acc_phase, abort_flag, p.dev_status, DEV_TIMEOUT_EPILOGUE, lane))
         break;
       tc_fence_after_sync();
-      const int row = m_blk * BM + quarter * 32 + lane;
+      const int row0 = m_blk * BM + quarter * 32;
+      const int row = row0 + lane;
+      const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      if (!e.swiglu) {
+      // Output columns of this tile, one 128-byte row segment (CHUNK columns) at a time.
+      constexpr int CHUNK = OUT_F32 ? 32 : 64;
+      const int out_cols = e.swiglu ? BN / 2 : BN;
+      const int out_col_base = n_blk * out_cols;
+      const int units = out_cols / CHUNK;
 #pragma unroll 1
-        for (int chunk = 0; chunk < BN / 32; ++chunk) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(taddr + chunk * 32, r);
+      for (int u = 0; u < units; ++u) {
+        const int col0 = out_col_base + u * CHUNK;
+        const bool active = row0 < p.M && col0 < p.n_out;  // warp-uniform: block intersects D
+        float v[CHUNK];
+        uint4 cseg[8], rseg[8];
+        const bool use_c = e.C != nullptr && active;
+        const bool use_r = e.R != nullptr && active;
+        if (!e.swiglu) {
+          uint32_t raw[CHUNK];
+#pragma unroll
+          for (int h = 0; h < CHUNK / 32; ++h) {
+            uint32_t(&part)[32] = *reinterpret_cast<uint32_t(*)[32]>(&raw[h * 32]);
+            tmem_ld_32x32b_x32(taddr + u * CHUNK + h * 32, part);
+          }
+          // C / residual rows travel while the tensor-memory load is in flight
+          if (use_c) load_row_segment<OUT_F32>(cseg, e.C, row_ok ? static_cast<int64_t>(row) * e.ldc + col0 : 0, row_ok ? col0 : p.n_out, p.n_out);
+          if (use_r) load_row_segment<OUT_F32>(rseg, e.R, row_ok ? static_cast<int64_t>(row) * e.ldr + col0 : 0, row_ok ? col0 : p.n_out, p.n_out);
           tmem_ld_wait();
-          const int col0 = n_blk * BN + chunk * 32;
-          if (row < p.M) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int c = col0 + g * 8;
-              if (c < p.N) {
-                float v[8];
+          for (int i = 0; i < CHUNK; ++i) v[i] = __uint_as_float(raw[i]);
+        } else {
+          // B columns of this tile are [gate (BN/2) | up (BN/2)]: D = silu(gate) * up.
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
-                if (e.C) {
-                  float cv[8];
-                  load8_as_f32(e.C, e.c_dtype, static_cast<int64_t>(row) * e.ldc + c, cv);
+          for (int h = 0; h < CHUNK / 32; ++h) {
+            uint32_t g_[32], u_[32];
+            tmem_ld_32x32b_x32(taddr + u * CHUNK + h * 32, g_);
+            tmem_ld_32x32b_x32(taddr + BN / 2 + u * CHUNK + h * 32, u_);
+            tmem_ld_wait();
 #pragma unroll
-                  for (int i = 0; i < 8; ++i) v[i] += cv[i];
-                }
-                if (e.bias) {
-                  float bv[8];
-                  load8_as_f32(e.bias, e.bias_dtype, c, bv);
+            for (int i = 0; i < 32; ++i) v[h * 32 + i] = apply_act(__uint_as_float(g_[i]), LH_ACT_SILU) * __uint_as_float(u_[i]);
+          }
+        }
+        if (u == units - 1) {
+          // every accumulator column of this tile is now in registers
+          tc_fence_before_sync();
+          mbar_arrive(&tmem_empty[buf]);
+        }
+        if (!active) continue;
+        if (!e.swiglu) {
+          if (use_c) add_row_segment<OUT_F32>(v, cseg);
+          if (e.bias) {
 #pragma unroll
-                  for (int i = 0; i < 8; ++i) v[i] += bv[i];
-                }
-                if (e.act != LH_ACT_NONE) {
+            for (int g = 0; g < CHUNK / 8; ++g) {
+              if (col0 + g * 8 < p.n_out) {
+                float bv[8];
+                load8_as_f32(e.bias, e.bias_dtype, col0 + g * 8, bv);
 #pragma unroll
-                  for (int i = 0; i < 8; ++i) v[i] = apply_act(v[i], e.act);
-                }
-                if (e.R) {
-                  float rv[8];
-                  load8_as_f32(e.R, e.r_dtype, static_cast<int64_t>(row) * e.ldr + c, rv);
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) v[i] += rv[i];
-                }
-                store8_from_f32(e.D, e.d_dtype, static_cast<int64_t>(row) * e.ldd + c, v);
+                for (int i = 0; i < 8; ++i) v[g * 8 + i] += bv[i];
               }
             }
           }
+          activate_block(v, e.act);
+          if (use_r) add_row_segment<OUT_F32>(v, rseg);
         }
-      } else {
-        // B columns of this tile are [gate(BN/2) | up(BN/2)]; D has N/2 columns.
-        constexpr int HALF = BN / 2;
-#pragma unroll 1
-        for (int chunk = 0; chunk < HALF / 32; ++chunk) {
-          uint32_t g_[32], u_[32];
-          tmem_ld_32x32b_x32(taddr + chunk * 32, g_);
-          tmem_ld_32x32b_x32(taddr + HALF + chunk * 32, u_);
-          tmem_ld_wait();
-          const int col0 = n_blk * HALF + chunk * 32;
-          if (row < p.M) {
+        uint8_t* sb = stage_bufs + sbuf * STAGING_BUF_BYTES;
+        if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer is done
+        __syncwarp();
+        if (!OUT_F32) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int c = col0 + g * 8;
-              if (c < p.N / 2) {
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float gate = __uint_as_float(g_[g * 8 + i]);
-                  const float up = __uint_as_float(u_[g * 8 + i]);
-                  v[i] = apply_act(gate, LH_ACT_SILU) * up;
-                }
-                store8_from_f32(e.D, e.d_dtype, static_cast<int64_t>(row) * e.ldd + c, v);
-              }
-            }
+          for (int j = 0; j < 8; ++j) {
+            uint4 q;
+            q.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+            q.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+            q.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+            q.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+            stage_chunk(sb, lane, j, q);
           }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            stage_chunk(sb, lane, j, make_uint4(__float_as_uint(v[j * 4]), __float_as_uint(v[j * 4 + 1]), __float_as_uint(v[j * 4 + 2]), __float_as_uint(v[j * 4 + 3])));
         }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tmD, sb, col0, row0);
+          bulk_commit_group();
+        }
+        sbuf ^= 1;
       }
-      tc_fence_before_sync();
-      mbar_arrive(&tmem_empty[buf]);
     }
+    if (lane == 0) bulk_wait_group<0>();  // all stores of this warp have landed
   }
 
   // ------------------------------------------------------------------ tear-down
@@ -292,10 +392,11 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
-template <int BN, bool B_KMAJOR, int STAGES>
+template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32>
 int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi) {
   using L = SmemLayout<BN, STAGES>;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmD;
+  const int n_out = epi.swiglu ? pr.N / 2 : pr.N;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(pr.K), static_cast<uint64_t>(pr.M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(pr.sam) * 2};
@@ -316,27 +417,46 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi) {
     int rc = encode_tensor_map(ctx, &tmB, LH_BF16, 2, const_cast<void*>(pr.B), dims, strides, box, 1);
     if (rc) return rc;
   }
+  {
+    const uint64_t esz = OUT_F32 ? 4 : 2;
+    const uint64_t dims[2] = {static_cast<uint64_t>(n_out), static_cast<uint64_t>(pr.M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(pr.sdm) * esz};
+    const uint32_t box[2] = {OUT_F32 ? 32u : 64u, 32u};
+    int rc = encode_tensor_map(ctx, &tmD, pr.d_dtype, 2, pr.D, dims, strides, box, 1);
+    if (rc) return rc;
+  }
   GemmTcParams p;
   p.M = pr.M;
   p.N = pr.N;
   p.K = pr.K;
+  p.n_out = n_out;
   p.num_m_blocks = (pr.M + BM - 1) / BM;
   p.num_n_blocks = (pr.N + BN - 1) / BN;
   p.num_k_blocks = (pr.K + BK - 1) / BK;
   p.epi = epi;
   p.dev_status = ctx->dev_status;
-  auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES>;
+  auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES, OUT_F32>;
   LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
   const int grid = num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count;
-  kernel<<<grid, NUM_THREADS, L::DYN_BYTES, ctx->stream>>>(tmA, tmB, p);
+  kernel<<<grid, NUM_THREADS, L::DYN_BYTES, ctx->stream>>>(tmA, tmB, tmD, p);
   LH_CHECK_LAUNCH(ctx, "gemm_bf16_tc_kernel");
   return LH_OK;
 }
 
+template <bool B_KMAJOR, bool OUT_F32>
+int launch_bn(lh_ctx* ctx, const GemmProblem& p, const EpiParams& epi, int bn) {
+  switch (bn) {
+    case 256: return launch_variant<256, B_KMAJOR, 4, OUT_F32>(ctx, p, epi);
+    case 192: return launch_variant<192, B_KMAJOR, 4, OUT_F32>(ctx, p, epi);
+    case 128: return launch_variant<128, B_KMAJOR, 6, OUT_F32>(ctx, p, epi);
+    default: return launch_variant<64, B_KMAJOR, 8, OUT_F32>(ctx, p, epi);
+  }
+}
+
 int pick_bn(const lh_ctx* ctx, const GemmProblem& p) {
   if (p.flags & LH_GEMM_SWIGLU) return 256;
-  static const char* env = getenv("LH_B200_GEMM_BN");
+  const char* env = getenv("LH_B200_GEMM_BN");  // tuning override, read per call
   if (env) {
     const int v = atoi(env);
     if (v == 64 || v == 128 || v == 192 || v == 256) return v;
@@ -381,15 +501,15 @@ int gemm_tc_bf16_supported(const lh_ctx* ctx, const GemmProblem& p) {
   const int n_out = (p.flags & LH_GEMM_SWIGLU) ? p.N / 2 : p.N;
   if ((p.flags & LH_GEMM_SWIGLU) && ((p.N % 256) != 0 || p.C || p.bias || p.R)) return 0;
   if (p.N % 8) return 0;
-  // Epilogue operands use 8-element vectors.
+  // D goes out through a tensor map; C / bias / residual use 8-element vectors.
   if (p.d_dtype != LH_BF16 && p.d_dtype != LH_F32) return 0;
   if (p.sdn != 1 || (p.sdm % 8) != 0 || p.sdm < n_out || !aligned16(p.D)) return 0;
   if (p.C) {
-    if (p.c_dtype != LH_BF16 && p.c_dtype != LH_F32) return 0;
+    if (p.c_dtype != p.d_dtype) return 0;  // the epilogue reads C rows as D-typed 128-byte segments
     if (p.scn != 1 || (p.scm % 8) != 0 || !aligned16(p.C)) return 0;
   }
   if (p.R) {
-    if (p.r_dtype != LH_BF16 && p.r_dtype != LH_F32) return 0;
+    if (p.r_dtype != p.d_dtype) return 0;
     if (p.srn != 1 || (p.srm % 8) != 0 || !aligned16(p.R)) return 0;
   }
   if (p.bias) {
@@ -408,22 +528,10 @@ int gemm_tc_bf16_launch(lh_ctx* ctx, const GemmProblem& p) {
   epi.act = p.act;
   epi.swiglu = (p.flags & LH_GEMM_SWIGLU) ? 1 : 0;
   const bool b_kmajor = (p.sbk == 1 && p.N > 1 && p.sbn >= p.K);
+  const bool out_f32 = p.d_dtype == LH_F32;
   const int bn = pick_bn(ctx, p);
-  if (b_kmajor) {
-    switch (bn) {
-      case 256: return launch_variant<256, true, 4>(ctx, p, epi);
-      case 192: return launch_variant<192, true, 5>(ctx, p, epi);
-      case 128: return launch_variant<128, true, 6>(ctx, p, epi);
-      default: return launch_variant<64, true, 8>(ctx, p, epi);
-    }
-  } else {
-    switch (bn) {
-      case 256: return launch_variant<256, false, 4>(ctx, p, epi);
-      case 192: return launch_variant<192, false, 5>(ctx, p, epi);
-      case 128: return launch_variant<128, false, 6>(ctx, p, epi);
-      default: return launch_variant<64, false, 8>(ctx, p, epi);
-    }
-  }
+  if (b_kmajor) return out_f32 ? launch_bn<true, true>(ctx, p, epi, bn) : launch_bn<true, false>(ctx, p, epi, bn);
+  return out_f32 ? launch_bn<false, true>(ctx, p, epi, bn) : launch_bn<false, false>(ctx, p, epi, bn);
 }
 
 int gemm_tc_tf32x3_supported(const lh_ctx*, const GemmProblem&) { return 0; }
