@@ -464,7 +464,7 @@ int pick_bn(const lh_ctx* ctx, const GemmProblem& p) {
   // Cost model: waves of tiles over the SMs times the per-tile time; narrower tiles
   // re-read A more often per flop, which the relative efficiencies account for.
   const int cand[3] = {256, 192, 128};
-  const double eff[3] = {1.0, 0.97, 0.86};
+  const double eff[3] = {1.0, 0.88, 0.72};  // measured on 4096 x 4096 x K problems
   const int num_m = (p.M + BM - 1) / BM;
   int best = 256;
   double best_cost = 1e300;
