@@ -83,7 +83,7 @@ def main(argv=None) -> int:
     except KeyboardInterrupt:
         print("\nInterrupted", file=sys.stderr)
         return 130
-    except (FileNotFoundError, OSError, ValueError) as exc:
+    except (FileNotFoundError, OSError, ValueError, RuntimeError) as exc:  # RuntimeError: no GPU / CUDA failure
         print(f"Error: {exc}", file=sys.stderr)
         return 1
 

@@ -1,0 +1,296 @@
+"""Parity of the CUDA kernels, called through the C ABI, against the CPU oracle on the same
+seeded inputs. Tolerances: max |out - ref| / max |ref| <= 1e-5 for f32, <= 2e-2 for bf16
+operands with f32 accumulation (oracle/check.py)."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import build as oracle_build
+from oracle import inputs as I
+from oracle import reference_ops as R
+from oracle.check import TOL_BF16, TOL_F32, max_rel_err
+
+from lighthouse_b200 import _native as N
+
+pytestmark = pytest.mark.gpu
+
+ACT = {"none": N.ACT_NONE, "relu": N.ACT_RELU, "gelu": N.ACT_GELU_ERF, "gelu_tanh": N.ACT_GELU_TANH, "silu": N.ACT_SILU}
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)) if isinstance(a, np.ndarray) else a
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda()
+
+
+def host(t):
+    return t.detach().float().cpu().numpy()
+
+
+# ------------------------------------------------------------------------------------ f32 GEMM
+@pytest.mark.parametrize("shape", [(16, 32, 64), (1, 1, 1), (130, 70, 33), (257, 129, 100)])
+def test_gemm_f32_matches_loop_nest(ctx, shape):
+    m, n, k = shape
+    a, b, c = I.gemm_f32_uniform(m, n, k, seed=m + n)
+    c = np.random.RandomState(1).rand(m, n).astype(np.float32)
+    ref = oracle_build.matmul_loops(a, b, c)
+    d = dev(c.copy())
+    ctx.gemm(d, dev(a), dev(b), c=d)
+    ctx.sync()
+    assert max_rel_err(host(d), ref) <= TOL_F32
+
+
+def test_gemm_f32_config1_full_size(ctx):
+    """Config 1: 1024^3, A, B ~ U(-1, 1), zero C; the C loop-nest oracle is the reference."""
+    a, b, c = I.gemm_f32_uniform(1024, 1024, 1024, seed=1)
+    ref = oracle_build.matmul_loops(a, b, c)
+    d = dev(c)
+    ctx.gemm(d, dev(a), dev(b))
+    ctx.sync()
+    assert max_rel_err(host(d), ref) <= TOL_F32
+    # strided views: A^T given as a transposed view, same answer
+    d2 = torch.zeros_like(d)
+    ctx.gemm(d2, dev(np.ascontiguousarray(a.T)).t(), dev(b))
+    ctx.sync()
+    assert max_rel_err(host(d2), ref) <= TOL_F32
+
+
+def test_gemm_empty_and_degenerate(ctx):
+    d = torch.full((4, 8), 3.0, device="cuda")
+    ctx.gemm(d, torch.zeros(4, 0, device="cuda"), torch.zeros(0, 8, device="cuda"))
+    ctx.sync()
+    assert float(d.abs().max()) == 0.0
+    ctx.gemm(torch.zeros(0, 8, device="cuda"), torch.zeros(0, 4, device="cuda"), torch.zeros(4, 8, device="cuda"))
+    with pytest.raises(ValueError):
+        ctx.gemm(torch.zeros(4, 8, device="cuda"), torch.zeros(4, 5, device="cuda"), torch.zeros(6, 8, device="cuda"))
+    with pytest.raises(ValueError):
+        ctx.gemm(torch.zeros(4, 8), torch.zeros(4, 5), torch.zeros(5, 8))  # host tensors: no CPU path
+
+
+# ---------------------------------------------------------------------------- bf16 tensor-core GEMM
+@pytest.mark.parametrize("layout", ["nn", "nt"])
+@pytest.mark.parametrize("shape,out", [((128, 256, 64), "bf16"), ((384, 768, 512), "bf16"), ((1000, 1000, 1000), "f32"), ((777, 1000, 520), "bf16"), ((130, 72, 64), "f32"), ((4096, 4096, 256), "bf16")])
+def test_gemm_bf16_bias_relu(ctx, layout, shape, out):
+    m, n, k = shape
+    a, b, bias = I.gemm_bf16_normal(m, n, k, seed=m)
+    a, b = a * 25, b * 25  # N(0, 0.5): keeps bf16 outputs well away from the subnormal range
+    A, B, bv = I.to_np(a), I.to_np(b), I.to_np(bias)
+    ref = R.gemm_epilogue(A, B, bias=bv, act="relu", out_dtype=out)
+    bd = dev(b.t().contiguous()).t() if layout == "nt" else dev(b)
+    d = torch.full((m, n), 7.0, device="cuda", dtype=torch.bfloat16 if out == "bf16" else torch.float32)
+    ctx.gemm(d, dev(a), bd, bias=dev(bias), act=N.ACT_RELU)
+    ctx.sync()
+    assert max_rel_err(host(d), ref) <= (TOL_BF16 if out == "bf16" else 1e-5)
+    # the CUDA-core kernel must agree with the tensor-core kernel
+    d2 = torch.empty_like(d)
+    ctx.gemm(d2, dev(a), bd, bias=dev(bias), act=N.ACT_RELU, flags=N.GEMM_FORCE_SIMT)
+    ctx.sync()
+    assert max_rel_err(host(d2), ref) <= (TOL_BF16 if out == "bf16" else 1e-5)
+
+
+@pytest.mark.parametrize("act", ["none", "gelu", "gelu_tanh", "silu"])
+@pytest.mark.parametrize("out", ["bf16", "f32"])
+def test_gemm_bf16_full_epilogue(ctx, act, out):
+    """acc = C + A.B + bias; act; + residual (in place over the residual buffer)."""
+    m, n, k = 300, 520, 192
+    a, b, bias = I.gemm_bf16_normal(m, n, k, seed=9)
+    a, b = a * 25, b * 25
+    tdt = torch.bfloat16 if out == "bf16" else torch.float32
+    g = torch.Generator().manual_seed(1)
+    c, res = torch.randn(m, n, generator=g).to(tdt), torch.randn(m, n, generator=g).to(tdt)
+    ref = R.gemm_epilogue(I.to_np(a), I.to_np(b), c=I.to_np(c), bias=I.to_np(bias), act=act, residual=I.to_np(res), out_dtype=out)
+    d = dev(res.clone())
+    ctx.gemm(d, dev(a), dev(b), c=dev(c), bias=dev(bias), residual=d, act=ACT[act])
+    ctx.sync()
+    assert max_rel_err(host(d), ref) <= (TOL_BF16 if out == "bf16" else 2e-5)
+
+
+def test_gemm_swiglu_epilogue(ctx):
+    from lighthouse_b200.workloads.decoder import pack_swiglu
+
+    m, k, f = 200, 256, 512
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16)
+    w1, w3 = (torch.randn(f, k, generator=g) * 0.1).to(torch.bfloat16), (torch.randn(f, k, generator=g) * 0.1).to(torch.bfloat16)
+    ref = R.swiglu_gemm(I.to_np(x), I.to_np(w1), I.to_np(w3), "bf16")
+    d = torch.empty(m, f, device="cuda", dtype=torch.bfloat16)
+    ctx.gemm(d, dev(x), dev(pack_swiglu(w1, w3)).t(), flags=N.GEMM_SWIGLU)
+    ctx.sync()
+    assert max_rel_err(host(d), ref) <= TOL_BF16
+
+
+def test_gemm_config2_full_size_properties(ctx):
+    """4096^3 bias + ReLU: sampled rows against the oracle, linearity in A, run-to-run
+    bitwise determinism."""
+    a, b, bias = I.gemm_bf16_normal(4096, 4096, 4096, seed=2)
+    ad, bd, biasd = dev(a), dev(b), dev(bias)
+    d = torch.empty(4096, 4096, device="cuda", dtype=torch.bfloat16)
+    ctx.gemm(d, ad, bd, bias=biasd, act=N.ACT_RELU)
+    ctx.sync()
+    rows = [0, 1, 127, 128, 2049, 4095]
+    ref = R.gemm_epilogue(I.to_np(a[rows]), I.to_np(b), bias=I.to_np(bias), act="relu", out_dtype="bf16")
+    assert max_rel_err(host(d[rows]), ref) <= TOL_BF16
+    d2 = torch.empty_like(d)
+    ctx.gemm(d2, ad, bd, bias=biasd, act=N.ACT_RELU)
+    ctx.sync()
+    assert torch.equal(d, d2)
+    # linearity: (2A).B == 2 (A.B) exactly (scaling by 2 is exact in bf16 and f32)
+    p1, p2 = torch.empty(4096, 4096, device="cuda"), torch.empty(4096, 4096, device="cuda")
+    ctx.gemm(p1, ad, bd)
+    ctx.gemm(p2, ad * 2, bd)
+    ctx.sync()
+    assert torch.equal(p1 * 2, p2)
+
+
+def test_batched_gemm(ctx):
+    g = torch.Generator().manual_seed(5)
+    a = (torch.randn(3, 40, 24, generator=g)).to(torch.bfloat16)
+    b = (torch.randn(3, 24, 56, generator=g)).to(torch.bfloat16)
+    d = torch.empty(3, 40, 56, device="cuda")
+    ctx.gemm(d, dev(a), dev(b))
+    ctx.sync()
+    assert max_rel_err(host(d), np.einsum("bmk,bkn->bmn", I.to_np(a), I.to_np(b))) <= 1e-5
+
+
+# --------------------------------------------------------------------------------- attention
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", [(1, 1, 1, 128, 128, 128), (1, 2, 1, 256, 256, 128), (2, 4, 2, 384, 384, 128), (1, 2, 2, 200, 333, 64), (2, 3, 3, 77, 77, 64), (1, 4, 1, 130, 514, 128)])
+def test_attention_bf16(ctx, shape, causal):
+    b, hq, hkv, sq, skv, d = shape
+    q, k, v = I.attention_qkv(b, hq, hkv, sq, skv, d, seed=sq + d)
+    ref = R.attention(I.to_np(q), I.to_np(k), I.to_np(v), causal=causal, io_dtype="bf16")
+    o = torch.full_like(q, 5.0).cuda()
+    ctx.attention_fwd(o, dev(q), dev(k), dev(v), d**-0.5, causal)
+    ctx.sync()
+    assert max_rel_err(host(o), ref) <= TOL_BF16
+
+
+def test_attention_strided_views_and_f32_output(ctx):
+    """q/k/v as head views of (tokens, 3C) rows — the layout the decoders use — no copies."""
+    bsz, s, h, hs = 2, 160, 4, 64
+    c = h * hs
+    g = torch.Generator().manual_seed(6)
+    qkv = torch.randn(bsz * s, 3 * c, generator=g).to(torch.bfloat16)
+    qkv_d = dev(qkv)
+    out = torch.zeros(bsz * s, c, device="cuda", dtype=torch.bfloat16)
+
+    def heads(t, col0):
+        return t[:, col0 : col0 + c].view(bsz, s, h, hs).permute(0, 2, 1, 3)
+
+    ctx.attention_fwd(heads(out, 0), heads(qkv_d, 0), heads(qkv_d, c), heads(qkv_d, 2 * c), hs**-0.5, True)
+    ctx.sync()
+    ref = R.attention(I.to_np(heads(qkv, 0)), I.to_np(heads(qkv, c)), I.to_np(heads(qkv, 2 * c)), causal=True, io_dtype="bf16")
+    assert max_rel_err(host(heads(out, 0)), ref) <= TOL_BF16
+
+
+def test_attention_f32_unfused_path(ctx):
+    q, k, v = (t.float() for t in I.attention_qkv(2, 2, 2, 64, 96, 32, seed=8))
+    o = torch.empty(2, 2, 64, 32, device="cuda")
+    ctx.attention_fwd(o, dev(q), dev(k), dev(v), 32**-0.5, False)
+    ctx.sync()
+    assert max_rel_err(host(o), R.attention_unfused_f32(I.to_np(q), I.to_np(k), I.to_np(v))) <= 1e-5
+
+
+def test_attention_config3_full_size_properties(ctx):
+    """B8 H16 S2048 D128: one (batch, head) slice against the oracle; determinism; V-linearity
+    (attention is linear in V: doubling V doubles O exactly)."""
+    q, k, v = I.attention_qkv(8, 16, 16, 2048, 2048, 128, seed=3)
+    qd, kd, vd = dev(q), dev(k), dev(v)
+    for causal in (False, True):
+        o = torch.empty_like(qd)
+        ctx.attention_fwd(o, qd, kd, vd, 128**-0.5, causal)
+        ctx.sync()
+        ref = R.attention(I.to_np(q[3:4, 5:6]), I.to_np(k[3:4, 5:6]), I.to_np(v[3:4, 5:6]), causal=causal, io_dtype="bf16")
+        assert max_rel_err(host(o[3:4, 5:6]), ref) <= TOL_BF16
+        o2 = torch.empty_like(qd)
+        ctx.attention_fwd(o2, qd, kd, vd * 2, 128**-0.5, causal)
+        ctx.sync()
+        assert torch.equal(o * 2, o2)
+        assert bool(torch.isfinite(o.float()).all())
+
+
+# ----------------------------------------------------------------------------------- row kernels
+@pytest.mark.parametrize("rows,n,xdt,odt", [(1000, 768, "f32", "bf16"), (64, 768, "f32", "f32"), (33, 100, "f32", "f32"), (17, 4096, "bf16", "bf16"), (5, 5000, "f32", "f32")])
+def test_layernorm(ctx, rows, n, xdt, odt):
+    rng = np.random.RandomState(rows)
+    x = R.round_to(rng.randn(rows, n).astype(np.float32) * 2 + 0.5, xdt)
+    g, b = rng.randn(n).astype(np.float32), rng.randn(n).astype(np.float32)
+    tdt = {"f32": torch.float32, "bf16": torch.bfloat16}
+    out = torch.empty(rows, n, device="cuda", dtype=tdt[odt])
+    ctx.layernorm(out, dev(x, tdt[xdt]), dev(g), dev(b), 1e-5)
+    ctx.sync()
+    assert max_rel_err(host(out), R.round_to(R.layernorm(x, g, b, 1e-5), odt)) <= (TOL_BF16 if odt == "bf16" else TOL_F32)
+
+
+@pytest.mark.parametrize("rows,n", [(512, 4096), (7, 128), (3, 1000)])
+def test_rmsnorm(ctx, rows, n):
+    rng = np.random.RandomState(n)
+    x = R.round_bf16(rng.randn(rows, n).astype(np.float32))
+    w = R.round_bf16(rng.randn(n).astype(np.float32))
+    out = torch.empty(rows, n, device="cuda", dtype=torch.bfloat16)
+    ctx.rmsnorm(out, dev(x, torch.bfloat16), dev(w, torch.bfloat16), 1e-5)
+    ctx.sync()
+    assert max_rel_err(host(out), R.rmsnorm(x, w, 1e-5, "bf16")) <= TOL_BF16
+    out32 = torch.empty(rows, n, device="cuda")
+    ctx.rmsnorm(out32, dev(x), None, 1e-5)
+    ctx.sync()
+    assert max_rel_err(host(out32), R.rmsnorm(x, None, 1e-5, "f32")) <= TOL_F32
+
+
+@pytest.mark.parametrize("rows,n", [(300, 1000), (64, 768), (2, 9000)])
+def test_softmax(ctx, rows, n):
+    x = np.random.RandomState(n).randn(rows, n).astype(np.float32) * 3
+    out = torch.empty(rows, n, device="cuda")
+    ctx.softmax(out, dev(x))
+    ctx.sync()
+    assert max_rel_err(host(out), R.softmax(x)) <= TOL_F32
+    np.testing.assert_allclose(host(out).sum(-1), 1.0, rtol=1e-5)
+
+
+def test_rope(ctx):
+    x = R.round_bf16(np.random.RandomState(2).randn(2, 300, 5, 128).astype(np.float32))
+    t = dev(x, torch.bfloat16)
+    ctx.rope(t, 10000.0, 0)
+    ctx.sync()
+    assert max_rel_err(host(t), R.rope(x, 10000.0, 0, "bf16")) <= TOL_BF16
+    t32 = dev(x)
+    ctx.rope(t32, 10000.0, 7)
+    ctx.sync()
+    assert max_rel_err(host(t32), R.rope(x, 10000.0, 7, "f32")) <= 1e-4  # angles up to ~300 rad in f32
+
+
+def test_elementwise_family_and_embedding(ctx):
+    rng = np.random.RandomState(4)
+    a, b, bias = rng.randn(64, 256).astype(np.float32), rng.randn(64, 256).astype(np.float32), rng.randn(256).astype(np.float32)
+    ad, bd, biasd = dev(a), dev(b), dev(bias)
+    out = torch.empty(64, 256, device="cuda")
+    cases = [
+        (N.EW_ADD, (ad, bd), {}, a + b), (N.EW_MUL, (ad, bd), {}, a * b), (N.EW_SUB, (ad, bd), {}, a - b), (N.EW_MAX, (ad, bd), {}, np.maximum(a, b)),
+        (N.EW_ADD_ACT, (ad, biasd), {"act": N.ACT_RELU}, np.maximum(a + bias, 0)), (N.EW_ACT, (ad,), {"act": N.ACT_GELU_ERF}, R.gelu_erf(a)),
+        (N.EW_SILU_MUL, (ad, bd), {}, R.silu(a) * b), (N.EW_SCALE, (ad,), {"scalar": 0.125}, a * 0.125), (N.EW_FILL, (), {"scalar": 2.5}, np.full_like(a, 2.5)),
+    ]
+    for kind, ops, kw, ref in cases:
+        ctx.elementwise(kind, out, *ops, **kw)
+        ctx.sync()
+        assert max_rel_err(host(out), ref) <= 1e-5, kind
+    # cast + transposing copy through strided views
+    o16 = torch.empty(256, 64, device="cuda", dtype=torch.bfloat16)
+    ctx.elementwise(N.EW_COPY, o16, ad.t())
+    ctx.sync()
+    assert np.array_equal(host(o16), R.round_bf16(a.T))
+    ids = rng.randint(0, 50, size=(3, 16))
+    wte, wpe = R.round_bf16(rng.randn(50, 32).astype(np.float32)), R.round_bf16(rng.randn(16, 32).astype(np.float32))
+    emb = torch.empty(48, 32, device="cuda")
+    ctx.embedding(emb, dev(ids.reshape(-1).astype(np.int32)), dev(wte, torch.bfloat16), dev(wpe, torch.bfloat16), 16)
+    ctx.sync()
+    assert max_rel_err(host(emb), R.embed(ids, wte, wpe)) <= 1e-6
+
+
+def test_launch_counter_and_status_word(ctx):
+    before = ctx.launch_count
+    t = torch.zeros(8, 8, device="cuda")
+    ctx.elementwise(N.EW_FILL, t, scalar=1.0)
+    ctx.sync()  # also reads the device status word: no bounded wait ran out
+    assert ctx.launch_count == before + 1 and float(t.sum()) == 64.0
