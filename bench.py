@@ -1,0 +1,552 @@
+#!/usr/bin/env python
+"""Benchmark of the sm_100a hot path. Prints ONE JSON line (rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload llama|nanogpt|gemm|attention]
+    python bench.py --impl reference ...      # the CPU baseline arm on the host cores
+
+Workloads (synthetic, seeded; shapes of the five benchmark configurations):
+  llama      (default) Llama-style decoder stack forward, bf16, 8 layers, d 4096, 32/8 heads,
+             FFN 14336, seq 4096, batch 4; tensor-parallel over the N GPUs (strong scaling);
+             metric = forward tokens/s. The line also carries the GEMM and attention kernel
+             throughputs measured in the same process at N=1 (`kernels`).
+  nanogpt    nanoGPT forward, 12 layers, d 768, seq 1024, batch 16, vocab 50304; TP up to 4,
+             8 GPUs = TP4 x 2 batch halves.
+  gemm       bf16 GEMM + bias + ReLU, M=N=K=4096 (`--k` for the K sweep); TFLOP/s.
+  attention  flash attention forward, B8 H16 S2048 D128 (`--causal`); TFLOP/s.
+
+`value` is measured with inputs resident in HBM; `e2e` is the same metric through host
+buffers: every step copies the inputs from pinned host memory and reads the result back.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PEAKS_FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(PEAKS_FALLBACK), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons of one GPU with nvidia-smi while the
+    timed region runs."""
+
+    FIELDS = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        fd, self.path = tempfile.mkstemp(suffix=".csv")
+        os.close(fd)
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL,
+            )
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, reasons, max_mhz, power = [], set(), None, []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    clocks.append(float(parts[0]))
+                    max_mhz = float(parts[1])
+                    power.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[3:7]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.remove(self.path)
+        if clocks:
+            # the busiest half of the samples: the sampler also sees the gaps between loops
+            busy = sorted(zip(power, clocks))[len(clocks) // 2 :]
+            out.update(sm_mhz=statistics.median(c for _, c in busy), sm_max_mhz=max_mhz, reasons=sorted(reasons), samples=len(clocks), power_w_max=max(power))
+        return out
+
+
+class Dist:
+    """torch.distributed plumbing: rendezvous, barrier, max over ranks, NCCL ids for groups."""
+
+    def __init__(self, n_gpus: int):
+        import torch
+
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != n_gpus and self.world > 1:
+            raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={self.world}")
+        if n_gpus > 1 and self.world == 1:
+            raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 bench.py --gpus N ...")
+        torch.cuda.set_device(self.local_rank)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+            self.dist = dist
+        else:
+            self.dist = None
+
+    def barrier(self):
+        import torch
+
+        torch.cuda.synchronize()
+        if self.dist:
+            self.dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(self, value: float) -> float:
+        if not self.dist:
+            return value
+        import torch
+
+        t = torch.tensor([value], device="cuda", dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(self, value: float) -> float:
+        if not self.dist:
+            return value
+        import torch
+
+        t = torch.tensor([value], device="cuda", dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return float(t.item())
+
+    def group_unique_id(self, group_leader: int, nccl_path):
+        """Every group leader creates an NCCL id; all ranks receive their leader's."""
+        from lighthouse_b200.context import nccl_unique_id
+
+        mine = nccl_unique_id(nccl_path) if self.rank == group_leader else None
+        ids = [None] * self.world
+        self.dist.all_gather_object(ids, mine)
+        return ids[group_leader]
+
+    def close(self):
+        if self.dist:
+            self.dist.destroy_process_group()
+
+
+def timed_loop(dist: Dist, stream, step, steps: int, warmup: int):
+    """W untimed steps, then exactly K steps between a barrier + synchronize on both sides,
+    timed with CUDA events on the launching stream; returns the max over ranks in ms."""
+    import torch
+
+    for _ in range(warmup):
+        step()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    stream.synchronize()
+    dist.barrier()
+    return dist.max_over_ranks(e0.elapsed_time(e1))
+
+
+def gemm_roofline(plan, op_ms, peaks, which):
+    """Roofline entry for the dominant kernel of a decoder step: all GEMM launches of one
+    step, algorithmic 2MNK flops over their CUDA-event durations."""
+    flops = sum(op.flops() for op in plan.ops if op.kind == "gemm")
+    ms = float(sum(t for op, t in zip(plan.ops, op_ms) if op.kind == "gemm"))
+    achieved = flops / (ms * 1e-3) / 1e12 if ms > 0 else 0.0
+    peak = peaks["bf16_tflops_sustained"]
+    share = {}
+    for op, t in zip(plan.ops, op_ms):
+        share[op.kind] = share.get(op.kind, 0.0) + float(t)
+    total = sum(share.values()) or 1.0
+    return {
+        "bound": "tensor", "kernel": "gemm_bf16_tc_kernel", "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
+        "frac": round(achieved / peak, 4), "peak_source": f"{which} cuBLAS bf16, sustained (kernel timed inside a long step)", "traffic": None,
+        "launches_per_step": sum(1 for op in plan.ops if op.kind == "gemm"),
+        "step_time_share": {k: round(v / total, 4) for k, v in sorted(share.items())},
+    }
+
+
+# ------------------------------------------------------------------------------- decoders
+def run_decoder(args, dist: Dist, which: str) -> dict:
+    import torch
+
+    from lighthouse_b200.context import CudaContext, find_torch_nccl
+    from lighthouse_b200.workloads import decoder as D
+    from lighthouse_b200.workloads.session import PlanSession
+    from lighthouse_b200.workloads import synthetic as I
+
+    n = dist.world
+    if which == "llama":
+        cfg = D.LlamaConfig(n_layer=args.layers or 8)
+        tp, dp = n, 1
+    else:
+        cfg = D.NanoGptConfig(n_layer=args.layers or 12)
+        tp = n if n <= 4 else 4  # 12 heads do not split 8 ways: 8 GPUs = TP4 x 2 batch halves
+        dp = n // tp
+        cfg = D.NanoGptConfig(n_layer=cfg.n_layer, batch=cfg.batch // dp)
+    D.check_tp(cfg, tp)
+    tp_rank, group = dist.rank % tp, dist.rank // tp
+    stream = torch.cuda.Stream()
+    ctx = CudaContext(dist.local_rank)
+    with torch.cuda.stream(stream):
+        ctx.use_torch_stream()
+    if tp > 1:
+        nccl = find_torch_nccl()
+        uid = dist.group_unique_id(group * tp, nccl)
+        ctx.comm_init(uid, tp_rank, tp, nccl)
+
+    # same seed on every rank, sliced locally: tp = n computes what tp = 1 computes
+    if which == "llama":
+        w = I.llama_weights(cfg.n_layer, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.ffn, seed=5)
+        weights = [t.cuda() for t in D.flatten_llama_args(D.shard_llama_weights(w, cfg, tp_rank, tp))]
+        plan = D.build_llama_plan(cfg, tp_rank, tp)
+        host_in = torch.randn(cfg.tokens, cfg.dim, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).pin_memory()
+        dev_in = host_in.cuda()
+        dev_out = torch.empty(cfg.tokens, cfg.dim, device="cuda", dtype=torch.bfloat16)
+    else:
+        w = I.nanogpt_weights(cfg.n_layer, cfg.n_embd, cfg.hidden, cfg.vocab, cfg.block_size, seed=4)
+        weights = [t.cuda() for t in D.flatten_nanogpt_args(D.shard_nanogpt_weights(w, cfg, tp_rank, tp))]
+        plan = D.build_nanogpt_plan(cfg, tp_rank, tp)
+        ids = torch.randint(0, cfg.vocab, (cfg.tokens * dp,), generator=torch.Generator().manual_seed(1)).to(torch.int32)
+        host_in = ids[group * cfg.tokens : (group + 1) * cfg.tokens].contiguous().pin_memory()
+        dev_in = host_in.cuda()
+        dev_out = torch.empty(cfg.tokens, cfg.vocab // tp, device="cuda", dtype=torch.float32)
+    del w
+    host_out = torch.empty(dev_out.shape, dtype=dev_out.dtype).pin_memory()
+    sess = PlanSession(plan, ctx=ctx)
+    dev_args = [dev_out, dev_in] + weights
+    total_tokens = cfg.tokens * dp
+
+    sampler = ClockSampler(dist.local_rank)
+    launches0 = ctx.launch_count
+    with torch.cuda.stream(stream):
+        sess.set_profiling(True)
+        sampler.start()
+        ms = timed_loop(dist, stream, lambda: sess.run(dev_args), args.steps, args.warmup)
+        launches = (ctx.launch_count - launches0) * args.steps // (args.steps + args.warmup)
+        op_ms = sess.op_times_ms()  # per-operator durations of the last timed step
+        sess.set_profiling(False)
+
+        def e2e_step():
+            dev_in.copy_(host_in, non_blocking=True)
+            sess.run(dev_args)
+            if dist.rank % tp == 0 or which == "nanogpt":
+                host_out.copy_(dev_out, non_blocking=True)
+
+        ms_e2e = timed_loop(dist, stream, e2e_step, args.steps, max(1, args.warmup // 2))
+        clocks = sampler.stop()
+    ctx.sync()  # raises if any kernel gave up on a bounded wait
+    h2d = host_in.numel() * host_in.element_size()
+    d2h = host_out.numel() * host_out.element_size() if (dist.rank % tp == 0 or which == "nanogpt") else 0
+    h2d_total, d2h_total = dist.sum_over_ranks(h2d), dist.sum_over_ranks(d2h)
+    peaks, source = load_peaks()
+    flops = cfg.flops_per_token() * total_tokens
+    step_s = ms / args.steps * 1e-3
+    res = {
+        "metric": f"{which}_decoder_forward_tokens_per_s", "value": round(total_tokens / step_s, 1), "unit": "tokens/s",
+        "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {
+            "workload": ("Llama-style decoder stack forward: %d layers, d_model %d, %d q / %d kv heads, head_dim %d, SwiGLU FFN %d, RMSNorm, RoPE, seq %d, batch %d" % (cfg.n_layer, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.seq, cfg.batch))
+            if which == "llama" else ("nanoGPT forward: %d layers, d_model %d, %d heads, GELU MLP x4, pre-LayerNorm, causal, seq %d, batch %d, vocab %d" % (cfg.n_layer, cfg.n_embd, cfg.n_head, cfg.seq, cfg.batch * dp, cfg.vocab)),
+            "parallelism": f"tp{tp}" + (f"xdp{dp}" if dp > 1 else ""), "tokens_per_step": total_tokens, "l2": "inputs_exceed_l2 (weights + activations >> 126 MB)",
+            "algorithmic_tflop_per_step": round(flops / 1e12, 3),
+        },
+        "model_tflops": round(flops / step_s / 1e12, 1), "model_frac_of_peak": round(flops / step_s / 1e12 / (n * peaks["bf16_tflops_sustained"]), 4),
+        "roofline": gemm_roofline(plan, op_ms, peaks, source),
+        "e2e": {"value": round(total_tokens / (ms_e2e / args.steps * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d_total), "d2h_bytes_per_step": int(d2h_total)},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    sess.close()
+    ctx.close()
+    return res
+
+
+# ---------------------------------------------------------------------------- single kernels
+L2_FLUSH_BYTES = 256 << 20  # > 126 MB of L2: overwritten between timed runs
+
+
+def kernel_gemm(ctx, peaks, source, K=4096, steps=20, warmup=5) -> dict:
+    """bf16 GEMM + bias + ReLU, M = N = 4096 (config 2): one launch per step, L2 flushed
+    between steps, one CUDA-event pair per launch."""
+    import torch
+
+    from lighthouse_b200.plan import ArgSpec, Plan
+    from lighthouse_b200.workloads import synthetic as I
+    from lighthouse_b200.workloads.session import PlanSession
+
+    M = N = 4096
+    a, b, bias = I.gemm_bf16_normal(M, N, K, seed=2)
+    plan = Plan("gemm_bias_relu", [ArgSpec((M, N), "bf16", "d"), ArgSpec((M, K), "bf16", "a"), ArgSpec((K, N), "bf16", "b"), ArgSpec((N,), "bf16", "bias")])
+    plan.gemm(plan.arg(0), plan.arg(1), plan.arg(2), bias=plan.arg(3), act="relu")
+    sess = PlanSession(plan, ctx=ctx)
+    d = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    dev_args = [d, a.cuda(), b.cuda(), bias.cuda()]
+    times = sess.benchmark(dev_args, nruns=steps, nwarmup=warmup, l2_flush_bytes=L2_FLUSH_BYTES)
+    sess.close()
+    flops = 2.0 * M * N * K
+    mean_s = float(times.mean())
+    achieved = flops / mean_s / 1e12
+    return {
+        "ms": round(mean_s * 1e3, 5), "best_ms": round(float(times.min()) * 1e3, 5), "tflops": round(achieved, 1), "shape": [M, N, K],
+        "roofline": {"bound": "tensor", "kernel": "gemm_bf16_tc_kernel", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{source} cuBLAS bf16, burst (kernel timed alone)", "traffic": None},
+        "host": (a, b, bias, d),
+    }
+
+
+def kernel_attention(ctx, peaks, source, causal=False, steps=20, warmup=5) -> dict:
+    """Flash attention forward, B8 H16 S2048 D128 bf16 (config 3)."""
+    import torch
+
+    from lighthouse_b200.plan import ArgSpec, Plan
+    from lighthouse_b200.workloads import synthetic as I
+    from lighthouse_b200.workloads.session import PlanSession
+
+    B, H, S, Dh = 8, 16, 2048, 128
+    q, k, v = I.attention_qkv(B, H, H, S, S, Dh, seed=3)
+    spec = lambda n: ArgSpec((B, H, S, Dh), "bf16", n)
+    plan = Plan("attention_fwd", [spec("o"), spec("q"), spec("k"), spec("v")])
+    plan.attention(plan.arg(0), plan.arg(1), plan.arg(2), plan.arg(3), Dh**-0.5, causal)
+    sess = PlanSession(plan, ctx=ctx)
+    o = torch.empty(B, H, S, Dh, device="cuda", dtype=torch.bfloat16)
+    times = sess.benchmark([o, q.cuda(), k.cuda(), v.cuda()], nruns=steps, nwarmup=warmup, l2_flush_bytes=L2_FLUSH_BYTES)
+    sess.close()
+    flops = 4.0 * B * H * S * S * Dh * (0.5 if causal else 1.0)
+    mean_s = float(times.mean())
+    achieved = flops / mean_s / 1e12
+    return {
+        "ms": round(mean_s * 1e3, 5), "tflops": round(achieved, 1), "causal": causal, "shape": [B, H, S, Dh],
+        "roofline": {"bound": "tensor", "kernel": "attn_fwd_tc_kernel", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{source} cuBLAS bf16, burst (kernel timed alone)", "traffic": None},
+        "host": (q, k, v, o),
+    }
+
+
+def run_kernel(args, dist: Dist, which: str) -> dict:
+    """N replicas of a single-kernel workload (the path does not shard: no collective)."""
+    import torch
+
+    from lighthouse_b200.context import CudaContext
+
+    peaks, source = load_peaks()
+    ctx = CudaContext(dist.local_rank)
+    sampler = ClockSampler(dist.local_rank)
+    sampler.start()
+    dist.barrier()
+    launches0 = ctx.launch_count
+    if which == "gemm":
+        r = kernel_gemm(ctx, peaks, source, K=args.k, steps=args.steps, warmup=args.warmup)
+        a, b, bias, d = r.pop("host")
+        host_ins, dev_out = [a.pin_memory(), b.pin_memory(), bias.pin_memory()], d
+        call = lambda ins: ctx.gemm(dev_out, ins[0], ins[1], bias=ins[2], act=1)
+        label = f"bf16 GEMM + bias + ReLU epilogue, M=N=4096, K={args.k}, A,B ~N(0,0.02), bias ~N(0,1), f32 accumulate, bf16 output"
+        metric = "gemm_bias_relu_tflops"
+    else:
+        r = kernel_attention(ctx, peaks, source, causal=args.causal, steps=args.steps, warmup=args.warmup)
+        q, k, v, o = r.pop("host")
+        host_ins, dev_out = [q.pin_memory(), k.pin_memory(), v.pin_memory()], o
+        call = lambda ins: ctx.attention_fwd(dev_out, ins[0], ins[1], ins[2], 128**-0.5, args.causal)
+        label = f"fused flash-attention forward, bf16, batch 8, heads 16, seq 2048, head_dim 128, {'causal' if args.causal else 'non-causal'}"
+        metric = "attention_fwd_tflops"
+    launches = (ctx.launch_count - launches0) * args.steps // (args.steps + args.warmup)
+    # end to end through host buffers: H2D of every operand, the kernel, D2H of the result
+    stream = torch.cuda.Stream()
+    dev_ins = [t.cuda() for t in host_ins]
+    host_out = torch.empty(dev_out.shape, dtype=dev_out.dtype).pin_memory()
+    with torch.cuda.stream(stream):
+        ctx.use_torch_stream()
+
+        def e2e_step():
+            for dt, ht in zip(dev_ins, host_ins):
+                dt.copy_(ht, non_blocking=True)
+            call(dev_ins)
+            host_out.copy_(dev_out, non_blocking=True)
+
+        ms_e2e = timed_loop(dist, stream, e2e_step, args.steps, 3)
+    clocks = sampler.stop()
+    ctx.sync()
+    ms = dist.max_over_ranks(r["ms"])
+    flops = r["tflops"] * r["ms"] * 1e9  # flops per launch
+    n = dist.world
+    res = {
+        "metric": metric, "value": round(n * flops / (ms * 1e-3) / 1e12, 1), "unit": "TFLOP/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": label, "parallelism": "replicas only (independent problems per GPU, no collective)" if n > 1 else "single GPU", "l2": f"L2 flushed between timed launches ({L2_FLUSH_BYTES >> 20} MiB overwritten)"},
+        "roofline": r["roofline"],
+        "e2e": {"value": round(n * flops / (ms_e2e / args.steps * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": int(n * sum(t.numel() * t.element_size() for t in host_ins)), "d2h_bytes_per_step": int(n * host_out.numel() * host_out.element_size())},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    ctx.close()
+    return res
+
+
+# ------------------------------------------------------------------ CPU baseline (oracle port)
+def cpu_sample(which: str, args) -> dict:
+    """One bounded sample of the workload on the host cores with the CPU oracle (a port of the
+    reference's semantics: its own CPU pipeline needs the MLIR bindings, which are not
+    installable here). Returns value in the workload's unit plus what was sampled."""
+    import numpy as np
+    import torch
+
+    from lighthouse_b200.workloads import synthetic as I
+    from oracle import build as oracle_build
+    from oracle import inputs as OI
+    from oracle import reference_ops as R
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    if which == "gemm":
+        rows = 256
+        a, b, bias = I.gemm_bf16_normal(rows, 4096, args.k, seed=2)
+        A, B, bv = OI.to_np(a), OI.to_np(b), OI.to_np(bias)
+        t0 = time.perf_counter()
+        oracle_build.matmul_bias_relu(A, B, bv, relu=True)
+        dt = time.perf_counter() - t0
+        return {"value": 2.0 * rows * 4096 * args.k / dt / 1e12, "unit": "TFLOP/s", "cores": oracle_build.num_threads(), "kind": "port",
+                "sample": f"{rows} of 4096 rows of the M=N=4096, K={args.k} problem, C loop nest (i,k,j) with OpenMP over rows, f32"}
+    if which == "attention":
+        q, k, v = I.attention_qkv(1, 2, 2, 2048, 2048, 128, seed=3)
+        t0 = time.perf_counter()
+        R.attention(OI.to_np(q), OI.to_np(k), OI.to_np(v), causal=args.causal, io_dtype="bf16")
+        dt = time.perf_counter() - t0
+        fl = 4.0 * 2 * 2048 * 2048 * 128 * (0.5 if args.causal else 1.0)
+        return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": "2 of the 128 (batch, head) pairs at seq 2048, head_dim 128, numpy f32"}
+    if which == "llama":
+        from lighthouse_b200.workloads.decoder import LlamaConfig
+
+        cfg = LlamaConfig()
+        seq = 512
+        w = OI.tree_to_np(I.llama_weights(1, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.ffn, seed=5))
+        x = np.random.RandomState(2).randn(1, seq, cfg.dim).astype(np.float32)
+        t0 = time.perf_counter()
+        R.llama_block(R.round_bf16(x), w["layers"][0], cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16")
+        dt = time.perf_counter() - t0
+        return {"value": seq / (dt * (args.layers or cfg.n_layer)), "unit": "tokens/s", "cores": cores, "kind": "port",
+                "sample": f"1 of {args.layers or cfg.n_layer} layers on batch 1 x seq {seq} (attention is cheaper per token than at seq 4096), numpy/BLAS f32 with bf16 rounding points; tokens/s scaled to the full layer count"}
+    from lighthouse_b200.workloads.decoder import NanoGptConfig
+
+    cfg = NanoGptConfig()
+    w = OI.tree_to_np(I.nanogpt_weights(2, cfg.n_embd, cfg.hidden, cfg.vocab, cfg.block_size, seed=4))
+    ids = np.random.RandomState(1).randint(0, cfg.vocab, size=(1, cfg.seq))
+    x = R.embed(ids, w["wte"], w["wpe"])
+    ts = []
+    for nl in (1, 2):
+        t0 = time.perf_counter()
+        R.nanogpt_forward(x, w["layers"][:nl], w["gf_g"], w["gf_b"], w["lmw"], w["lmb"], cfg.n_head, cfg.eps, True, "gelu", "bf16", 1)
+        ts.append(time.perf_counter() - t0)
+    layer = max(ts[1] - ts[0], 1e-6)
+    head = max(ts[0] - layer, 0.0)
+    nl = args.layers or cfg.n_layer
+    return {"value": cfg.seq / (nl * layer + head), "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"batch 1 x seq {cfg.seq}: per-layer time from a 1- and a 2-layer run, lm_head once; tokens/s composed for {nl} layers; numpy/BLAS f32 with bf16 rounding points"}
+
+
+METRICS = {"llama": "llama_decoder_forward_tokens_per_s", "nanogpt": "nanogpt_decoder_forward_tokens_per_s", "gemm": "gemm_bias_relu_tflops", "attention": "attention_fwd_tflops"}
+
+
+def reference_arm(args) -> int:
+    """`--impl reference`: the CPU baseline on the host cores, on rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0
+    for _ in range(min(args.warmup, 1)):
+        cpu_sample(args.workload, args)
+    t0 = time.perf_counter()
+    samples = [cpu_sample(args.workload, args) for _ in range(max(1, min(args.steps, 5)))]
+    dt = time.perf_counter() - t0
+    value = statistics.mean(s["value"] for s in samples)
+    s = samples[0]
+    line = {
+        "impl": "reference", "metric": METRICS[args.workload], "value": round(value, 6), "unit": s["unit"], "n_gpus": args.gpus, "steps": len(samples),
+        "warmup": min(args.warmup, 1), "ms_per_step": round(dt / len(samples) * 1e3, 2), "higher_is_better": True,
+        "scaling": "strong" if args.workload in ("llama", "nanogpt") else "weak", "vs_baseline": None, "dtype": "f32 arithmetic on bf16-rounded data", "data": "synthetic",
+        "config": {"workload": args.workload, "note": "the reference's own CPU pipeline (lh-run through the MLIR ExecutionEngine) is unavailable: mlir-python-bindings cannot be installed offline; this arm times the CPU oracle port of the same path"},
+        "cpu_baseline": {"value": round(value, 6), "unit": s["unit"], "cores": s["cores"], "kind": s["kind"], "sample": s["sample"]},
+        "e2e": {"value": round(value, 6), "unit": s["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=["llama", "nanogpt", "gemm", "attention"], default="llama")
+    ap.add_argument("--k", type=int, default=4096, help="K of the GEMM workload (sweep 1024..16384)")
+    ap.add_argument("--causal", action="store_true", help="causal mask for the attention workload")
+    ap.add_argument("--layers", type=int, default=0, help="override the decoder depth (0 = the configuration's)")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the GEMM / attention kernel lines of the decoder workloads")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    dist = Dist(args.gpus)
+    if args.workload in ("llama", "nanogpt"):
+        res = run_decoder(args, dist, args.workload)
+    else:
+        res = run_kernel(args, dist, args.workload)
+    if dist.rank == 0 and dist.world == 1:
+        if args.workload in ("llama", "nanogpt") and not args.no_kernels:
+            from lighthouse_b200.context import CudaContext
+
+            peaks, source = load_peaks()
+            ctx = CudaContext(dist.local_rank)
+            kernels = {}
+            g = kernel_gemm(ctx, peaks, source)
+            g.pop("host")
+            kernels["gemm_bias_relu_4096x4096x4096"] = g
+            for causal in (False, True):
+                a = kernel_attention(ctx, peaks, source, causal=causal)
+                a.pop("host")
+                kernels["attention_b8_h16_s2048_d128_" + ("causal" if causal else "full")] = a
+            ctx.close()
+            res["kernels"] = kernels
+        if not args.no_cpu_baseline:
+            s = cpu_sample(args.workload, args)
+            res["cpu_baseline"] = {"value": round(s["value"], 6), "unit": s["unit"], "cores": s["cores"], "kind": s["kind"], "sample": s["sample"]}
+    if dist.rank == 0:
+        print(json.dumps(res), flush=True)
+    dist.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

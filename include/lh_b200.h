@@ -297,6 +297,11 @@ int lh_b200_module_run(lh_module_t* m, void* const* arg_ptrs, int nargs);
  */
 int lh_b200_benchmark(lh_module_t* m, void* const* arg_ptrs, int nargs, double* times, int64_t nruns,
                       int64_t nwarmup, size_t l2_flush_bytes);
+/* Per-operator timing: with profiling on, module_run records a CUDA event on the context
+ * stream before the first operator and after each one; op_times waits for the last run and
+ * fills ms[i] with operator i's duration in milliseconds (n = number of operators). */
+int lh_b200_module_set_profiling(lh_module_t* m, int enable);
+int lh_b200_module_op_times(lh_module_t* m, float* ms, int n);
 /* Captures one module_run into a CUDA graph and replays it on later runs. */
 int lh_b200_module_use_graph(lh_module_t* m, int enable);
 

@@ -172,6 +172,8 @@ _PROTOTYPES = {
         [c_void_p, POINTER(c_void_p), c_int, POINTER(c_double), c_int64, c_int64, c_size_t],
     ),
     "lh_b200_module_use_graph": (c_int, [c_void_p, c_int]),
+    "lh_b200_module_set_profiling": (c_int, [c_void_p, c_int]),
+    "lh_b200_module_op_times": (c_int, [c_void_p, POINTER(c_float), c_int]),
 }
 
 EXPORTED_SYMBOLS = tuple(_PROTOTYPES)

@@ -529,6 +529,9 @@ struct lh_module {
   bool use_graph = false;
   cudaGraphExec_t graph_exec = nullptr;
   std::vector<void*> graph_args;
+  // per-operator timing: one event before the first operator and one after each
+  bool profiling = false;
+  std::vector<cudaEvent_t> op_events;
 };
 
 extern "C" int lh_b200_module_create(lh_ctx_t* ctx, const char* entry_name, const lh_arg_sig_t* args, int nargs,
@@ -569,6 +572,7 @@ extern "C" int lh_b200_module_destroy(lh_module_t* m) {
   if (!m) return LH_OK;
   cudaStreamSynchronize(m->ctx->stream);
   if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+  for (auto& e : m->op_events) cudaEventDestroy(e);
   for (void* t : m->temps)
     if (t) cudaFree(t);
   delete m;
@@ -598,6 +602,7 @@ static int run_ops(lh_module* m, void* const* arg_ptrs) {
     const lh_memref_t* o[LH_MAX_OPERANDS];
     for (int j = 0; j < LH_MAX_OPERANDS; ++j) o[j] = resolve(op.operands[j], mr[j]);
     int rc = LH_OK;
+    if (m->profiling && i == 0) cudaEventRecord(m->op_events[0], ctx->stream);
     switch (op.kind) {
       case LH_OP_GEMM: rc = lh_b200_gemm(ctx, o[0], o[1], o[2], o[3], o[4], o[5], op.i0, static_cast<uint32_t>(op.i1)); break;
       case LH_OP_ATTENTION: rc = lh_b200_attention_fwd(ctx, o[0], o[1], o[2], o[3], op.f0, op.i0); break;
@@ -616,6 +621,7 @@ static int run_ops(lh_module* m, void* const* arg_ptrs) {
       snprintf(msg, sizeof(msg), "%s", ctx->err);
       return set_error(ctx, rc, "op %zu (kind %d): %s", i, op.kind, msg);
     }
+    if (m->profiling) cudaEventRecord(m->op_events[i + 1], ctx->stream);
   }
   return LH_OK;
 }
@@ -654,6 +660,28 @@ extern "C" int lh_b200_module_run(lh_module_t* m, void* const* arg_ptrs, int nar
   }
   LH_CUDA_CHECK(ctx, cudaGraphLaunch(m->graph_exec, ctx->stream));
   ctx->launches += static_cast<int64_t>(m->ops.size());
+  return LH_OK;
+}
+
+extern "C" int lh_b200_module_set_profiling(lh_module_t* m, int enable) {
+  if (!m) return LH_ERR_INVALID;
+  lh_ctx* ctx = m->ctx;
+  if (enable && m->use_graph) return set_error(ctx, LH_ERR_INVALID, "per-operator timing is not available in graph mode");
+  if (enable && m->op_events.empty()) {
+    m->op_events.resize(m->ops.size() + 1);
+    for (auto& e : m->op_events) LH_CUDA_CHECK(ctx, cudaEventCreate(&e));
+  }
+  m->profiling = enable != 0;
+  return LH_OK;
+}
+
+extern "C" int lh_b200_module_op_times(lh_module_t* m, float* ms, int n) {
+  if (!m || !ms) return LH_ERR_INVALID;
+  lh_ctx* ctx = m->ctx;
+  if (m->op_events.empty() || n != static_cast<int>(m->ops.size()))
+    return set_error(ctx, LH_ERR_INVALID, "op_times: profiling was not enabled or n != number of operators");
+  LH_CUDA_CHECK(ctx, cudaEventSynchronize(m->op_events.back()));
+  for (int i = 0; i < n; ++i) LH_CUDA_CHECK(ctx, cudaEventElapsedTime(&ms[i], m->op_events[i], m->op_events[i + 1]));
   return LH_OK;
 }
 

@@ -54,6 +54,17 @@ class PlanSession:
         N.check(rc, self.ctx.handle, "lh_b200_benchmark")
         return times
 
+    def set_profiling(self, enable: bool = True) -> None:
+        N.check(self.ctx._lib.lh_b200_module_set_profiling(self.handle, int(enable)), self.ctx.handle, "lh_b200_module_set_profiling")
+
+    def op_times_ms(self) -> np.ndarray:
+        """Per-operator durations (ms) of the last run made with profiling on."""
+        n = len(self.plan.ops)
+        ms = np.zeros((n,), dtype=np.float32)
+        rc = self.ctx._lib.lh_b200_module_op_times(self.handle, ms.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), n)
+        N.check(rc, self.ctx.handle, "lh_b200_module_op_times")
+        return ms
+
     def close(self) -> None:
         if getattr(self, "handle", None):
             self.ctx._lib.lh_b200_module_destroy(self.handle)
