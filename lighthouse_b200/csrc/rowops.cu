@@ -1,9 +1,10 @@
 // HBM-bound row and elementwise kernels: LayerNorm, RMSNorm, row softmax, rotary
 // embedding, the elementwise family and the embedding gather.
 //
-// Row reductions keep one row per warp in registers (16-byte vector loads, warp
-// shuffles for the reductions, no shared memory); rows too long or not vectorisable
-// fall back to a block-per-row kernel that re-reads the row from L2.
+// Row reductions keep a row in the registers of one warp (or of 4 / 8 warps for long rows):
+// 16-byte vector loads, warp shuffles for the reductions, a few words of shared memory
+// only to combine warps; rows longer than 8192 elements or not vectorisable fall back to
+// a block-per-row kernel that re-reads the row from L2.
 #include "common.cuh"
 #include "epilogue.cuh"
 
@@ -39,18 +40,40 @@ struct RowParams {
   int mode;  // 0 layernorm, 1 rmsnorm, 2 softmax
 };
 
-// One warp per row; lane owns VPL vectors of 8 consecutive elements, vector v of
-// lane l covers columns [(v*32 + l)*8, +8).
-template <int VPL>
-__global__ void __launch_bounds__(128) row_warp_kernel(const RowParams p) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= p.rows) return;
+// A group of TPR threads per row (one warp, or 4 / 8 warps of a 256-thread block); thread t
+// of the group owns VPL vectors of 8 consecutive elements, vector i covering columns
+// [(i*TPR + t)*8, +8), so a row of up to TPR*VPL*8 elements lives in registers once.
+template <int VPL, int TPR>
+__global__ void __launch_bounds__(256) row_group_kernel(const RowParams p) {
+  constexpr int GROUPS = 256 / TPR;
+  constexpr int WARPS_PER_GROUP = TPR / 32;
+  __shared__ float red[2][8];
+  const int t = threadIdx.x % TPR;
+  const int group = threadIdx.x / TPR;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int64_t row = static_cast<int64_t>(blockIdx.x) * GROUPS + group;
+  const bool valid = row < p.rows;
+  if (!valid) row = p.rows - 1;  // keep every thread in the block-wide barriers
+  int phase = 0;
+  auto group_reduce = [&](float val, bool is_max) -> float {
+    val = is_max ? warp_max(val) : warp_sum(val);
+    if (WARPS_PER_GROUP == 1) return val;
+    if (lane == 0) red[phase][warp] = val;
+    __syncthreads();
+    float r = is_max ? -INFINITY : 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS_PER_GROUP; ++w) {
+      const float o = red[phase][group * WARPS_PER_GROUP + w];
+      r = is_max ? fmaxf(r, o) : r + o;
+    }
+    phase ^= 1;
+    return r;
+  };
   float v[VPL][8];
   const int64_t xoff = row * p.x_row_stride;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
-    const int c = (i * 32 + lane) * 8;
+    const int c = (i * TPR + t) * 8;
     if (c < p.n) {
       load8_as_f32(p.x, p.x_dtype, xoff + c, v[i]);
     } else {
@@ -66,7 +89,7 @@ __global__ void __launch_bounds__(128) row_warp_kernel(const RowParams p) {
     for (int i = 0; i < VPL; ++i)
 #pragma unroll
       for (int k = 0; k < 8; ++k) mx = fmaxf(mx, v[i][k]);
-    mx = warp_max(mx);
+    mx = group_reduce(mx, true);
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i)
@@ -75,7 +98,7 @@ __global__ void __launch_bounds__(128) row_warp_kernel(const RowParams p) {
         v[i][k] = __expf(v[i][k] - mx);
         sum += v[i][k];
       }
-    sum = warp_sum(sum);
+    sum = group_reduce(sum, false);
     const float inv = 1.f / sum;
 #pragma unroll
     for (int i = 0; i < VPL; ++i)
@@ -89,13 +112,13 @@ __global__ void __launch_bounds__(128) row_warp_kernel(const RowParams p) {
       for (int i = 0; i < VPL; ++i)
 #pragma unroll
         for (int k = 0; k < 8; ++k) s += v[i][k];
-      mean = warp_sum(s) * inv_n;
+      mean = group_reduce(s, false) * inv_n;
     }
     // second pass over registers: sum of squared deviations (biased variance)
     float sq = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
-      const int c = (i * 32 + lane) * 8;
+      const int c = (i * TPR + t) * 8;
       if (c < p.n) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -104,10 +127,10 @@ __global__ void __launch_bounds__(128) row_warp_kernel(const RowParams p) {
         }
       }
     }
-    const float rstd = rsqrtf(warp_sum(sq) * inv_n + p.eps);
+    const float rstd = rsqrtf(group_reduce(sq, false) * inv_n + p.eps);
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
-      const int c = (i * 32 + lane) * 8;
+      const int c = (i * TPR + t) * 8;
       if (c < p.n) {
         float g[8], bt[8];
         if (p.gamma) load8_as_f32(p.gamma, p.gamma_dtype, c, g);
@@ -125,12 +148,23 @@ __global__ void __launch_bounds__(128) row_warp_kernel(const RowParams p) {
       }
     }
   }
+  if (!valid) return;
   const int64_t ooff = row * p.out_row_stride;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
-    const int c = (i * 32 + lane) * 8;
+    const int c = (i * TPR + t) * 8;
     if (c < p.n) store8_from_f32(p.out, p.out_dtype, ooff + c, v[i]);
   }
+}
+
+template <int TPR>
+void launch_row_group(const RowParams& p, cudaStream_t stream) {
+  const int vpl = (p.n / 8 + TPR - 1) / TPR;
+  const unsigned blocks = static_cast<unsigned>((p.rows + (256 / TPR) - 1) / (256 / TPR));
+  if (vpl <= 1) row_group_kernel<1, TPR><<<blocks, 256, 0, stream>>>(p);
+  else if (vpl <= 2) row_group_kernel<2, TPR><<<blocks, 256, 0, stream>>>(p);
+  else if (vpl <= 3) row_group_kernel<3, TPR><<<blocks, 256, 0, stream>>>(p);
+  else row_group_kernel<4, TPR><<<blocks, 256, 0, stream>>>(p);
 }
 
 // Block per row, any length / alignment; three passes over the row.
@@ -231,20 +265,16 @@ int row_launch(lh_ctx* ctx, const lh_memref_t* out, const lh_memref_t* x, const 
   p.mode = mode;
   if (gamma && numel(gamma) != p.n) return set_error(ctx, LH_ERR_INVALID, "%s: scale length mismatch", what);
   if (beta && numel(beta) != p.n) return set_error(ctx, LH_ERR_INVALID, "%s: shift length mismatch", what);
-  bool vec = (p.n % 8) == 0 && p.n <= 32 * 8 * 16 && vec_ok(p.x, p.x_dtype, p.x_row_stride) &&
+  bool vec = (p.n % 8) == 0 && p.n <= 256 * 8 * 4 && vec_ok(p.x, p.x_dtype, p.x_row_stride) &&
              vec_ok(p.out, p.out_dtype, p.out_row_stride);
   if (gamma) vec = vec && vec_ok(p.gamma, p.gamma_dtype, 8) && is_contiguous(gamma);
   if (beta) vec = vec && vec_ok(p.beta, p.beta_dtype, 8) && is_contiguous(beta);
   if (vec) {
-    const int vpl = (p.n + 255) / 256;
-    const unsigned blocks = static_cast<unsigned>((p.rows + 3) / 4);
-    if (vpl <= 1) row_warp_kernel<1><<<blocks, 128, 0, ctx->stream>>>(p);
-    else if (vpl <= 2) row_warp_kernel<2><<<blocks, 128, 0, ctx->stream>>>(p);
-    else if (vpl <= 3) row_warp_kernel<3><<<blocks, 128, 0, ctx->stream>>>(p);
-    else if (vpl <= 4) row_warp_kernel<4><<<blocks, 128, 0, ctx->stream>>>(p);
-    else if (vpl <= 8) row_warp_kernel<8><<<blocks, 128, 0, ctx->stream>>>(p);
-    else row_warp_kernel<16><<<blocks, 128, 0, ctx->stream>>>(p);
-    LH_CHECK_LAUNCH(ctx, "row_warp_kernel");
+    const int nvec = p.n / 8;
+    if (nvec <= 32 * 4) launch_row_group<32>(p, ctx->stream);
+    else if (nvec <= 128 * 4) launch_row_group<128>(p, ctx->stream);
+    else launch_row_group<256>(p, ctx->stream);
+    LH_CHECK_LAUNCH(ctx, "row_group_kernel");
   } else {
     if (p.rows > 0x7fffffffLL) return set_error(ctx, LH_ERR_UNSUPPORTED, "%s: too many rows", what);
     row_block_kernel<<<static_cast<unsigned>(p.rows), 256, 0, ctx->stream>>>(p);
@@ -262,26 +292,38 @@ struct RopeParams {
   int pos0;
 };
 __global__ void __launch_bounds__(256) rope_kernel(const RopeParams p) {
+  // One thread per (position, pair): the angle and its sine / cosine are computed once and
+  // reused for every batch entry and head.
   const int half = p.D / 2;
-  const int64_t total = static_cast<int64_t>(p.B) * p.S * p.H * half;
+  const int64_t total = static_cast<int64_t>(p.S) * half;
   for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int i = static_cast<int>(idx % half);
-    int64_t t = idx / half;
-    const int h = static_cast<int>(t % p.H);
-    t /= p.H;
-    const int s = static_cast<int>(t % p.S);
-    const int b = static_cast<int>(t / p.S);
+    const int s = static_cast<int>(idx / half);
     // freqs = 1 / theta^(2i/D); angle = position * freq, all in f32 as torch computes it
     const float freq = 1.0f / powf(p.theta, static_cast<float>(2 * i) / static_cast<float>(p.D));
     const float ang = static_cast<float>(p.pos0 + s) * freq;
     float sn, cs;
     sincosf(ang, &sn, &cs);
-    const int64_t off = b * p.sb + s * p.ss + h * p.sh + 2 * i;
-    const float x0 = load_as_f32(p.x, p.dtype, off);
-    const float x1 = load_as_f32(p.x, p.dtype, off + 1);
-    store_from_f32(p.x, p.dtype, off, x0 * cs - x1 * sn);
-    store_from_f32(p.x, p.dtype, off + 1, x0 * sn + x1 * cs);
+    for (int b = 0; b < p.B; ++b) {
+      for (int h = 0; h < p.H; ++h) {
+        const int64_t off = b * p.sb + s * p.ss + h * p.sh + 2 * i;
+        if (p.dtype == LH_BF16) {
+          __nv_bfloat162* ptr = reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(p.x) + off);
+          const float2 x = __bfloat1622float2(*ptr);
+          *ptr = __floats2bfloat162_rn(x.x * cs - x.y * sn, x.x * sn + x.y * cs);
+        } else if (p.dtype == LH_F32) {
+          float2* ptr = reinterpret_cast<float2*>(static_cast<float*>(p.x) + off);
+          const float2 x = *ptr;
+          *ptr = make_float2(x.x * cs - x.y * sn, x.x * sn + x.y * cs);
+        } else {
+          const float x0 = load_as_f32(p.x, p.dtype, off);
+          const float x1 = load_as_f32(p.x, p.dtype, off + 1);
+          store_from_f32(p.x, p.dtype, off, x0 * cs - x1 * sn);
+          store_from_f32(p.x, p.dtype, off + 1, x0 * sn + x1 * cs);
+        }
+      }
+    }
   }
 }
 
@@ -404,8 +446,10 @@ int rope_launch(lh_ctx* ctx, const lh_memref_t* x, float theta, int pos0) {
   p.B = (int)x->shape[0]; p.S = (int)x->shape[1]; p.H = (int)x->shape[2]; p.D = (int)x->shape[3];
   p.sb = x->strides[0]; p.ss = x->strides[1]; p.sh = x->strides[2];
   p.theta = theta; p.pos0 = pos0;
-  const int64_t total = numel(x) / 2;
-  if (total == 0) return LH_OK;
+  if (numel(x) == 0) return LH_OK;
+  if ((p.sb | p.ss | p.sh) & 1 || (reinterpret_cast<uintptr_t>(p.x) & 7))
+    return set_error(ctx, LH_ERR_UNSUPPORTED, "rope: strides must be even and the base 8-byte aligned");
+  const int64_t total = static_cast<int64_t>(p.S) * (p.D / 2);
   rope_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(p);
   LH_CHECK_LAUNCH(ctx, "rope_kernel");
   return LH_OK;
