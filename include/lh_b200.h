@@ -167,6 +167,24 @@ int lh_b200_gemm(lh_ctx_t* ctx, const lh_memref_t* d, const lh_memref_t* a, cons
 int lh_b200_attention_fwd(lh_ctx_t* ctx, const lh_memref_t* o, const lh_memref_t* q, const lh_memref_t* k,
                           const lh_memref_t* v, float scale, int causal);
 
+/*
+ * The same attention for callers that are not allowed to allocate device memory: a
+ * process whose memory pool owns every free byte, a latency-critical thread that must not
+ * hit the device-wide synchronisation an allocation may imply, anything running behind a
+ * "no allocation after warm-up" rule. It has no counterpart in the reference.
+ * It always takes the un-fused route (batched Q K^T, scale, mask, row softmax, batched P V)
+ * and keeps the f32 score matrix of one head in a 4 MiB buffer built into the library
+ * (every GPU that loads the library holds it until the process exits), so it needs
+ * Sq * Skv <= 1,048,576 and returns LH_ERR_UNSUPPORTED with a message beyond that.
+ * Operands are rank-4 (B, H, S, D) views as above; results match lh_b200_attention_fwd's
+ * un-fused path. It calls no cudaMalloc / cudaFree and no allocating library routine.
+ * The first call on a device looks up the buffer's device address; make that first call
+ * outside any stream capture. All calls share the one buffer: two calls whose kernels can
+ * overlap on the GPU (different streams or contexts on one device) race on it.
+ */
+int lh_b200_attention_fwd_noalloc(lh_ctx_t* ctx, const lh_memref_t* o, const lh_memref_t* q, const lh_memref_t* k,
+                                  const lh_memref_t* v, float scale, int causal);
+
 /* out = (x - mean) * rsqrt(var + eps) * gamma + beta over the last dim, biased
  * variance, two-pass: emit_layer_norm_generics,
  * lighthouse/ingress/mlir_gen/gpu_layer_norm_payload.py:15-87. gamma/beta may be NULL. */

@@ -139,6 +139,7 @@ _PROTOTYPES = {
         [c_void_p] + [POINTER(MemRef)] * 6 + [c_int, c_uint32],
     ),
     "lh_b200_attention_fwd": (c_int, [c_void_p] + [POINTER(MemRef)] * 4 + [c_float, c_int]),
+    "lh_b200_attention_fwd_noalloc": (c_int, [c_void_p] + [POINTER(MemRef)] * 4 + [c_float, c_int]),
     "lh_b200_layernorm": (c_int, [c_void_p] + [POINTER(MemRef)] * 4 + [c_float]),
     "lh_b200_rmsnorm": (c_int, [c_void_p] + [POINTER(MemRef)] * 3 + [c_float]),
     "lh_b200_softmax": (c_int, [c_void_p] + [POINTER(MemRef)] * 2),

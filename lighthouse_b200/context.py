@@ -143,6 +143,14 @@ class CudaContext:
         rc = self._lib.lh_b200_attention_fwd(self.handle, _ref(mo), _ref(mq), _ref(mk), _ref(mv), float(scale), int(bool(causal)))
         N.check(rc, self.handle, "lh_b200_attention_fwd")
 
+    def attention_fwd_noalloc(self, o, q, k, v, scale: float, causal: bool = False) -> None:
+        """Un-fused attention that performs no device allocation (score scratch lives in the
+        library image; Sq * Skv <= 1 Mi). For callers whose memory is fully owned by their own
+        pool or that must not allocate once warm."""
+        mo, mq, mk, mv = (as_memref(x) for x in (o, q, k, v))
+        rc = self._lib.lh_b200_attention_fwd_noalloc(self.handle, _ref(mo), _ref(mq), _ref(mk), _ref(mv), float(scale), int(bool(causal)))
+        N.check(rc, self.handle, "lh_b200_attention_fwd_noalloc")
+
     def layernorm(self, out, x, gamma=None, beta=None, eps: float = 1e-5) -> None:
         mo, mx, mg, mb = (as_memref(t) for t in (out, x, gamma, beta))
         N.check(self._lib.lh_b200_layernorm(self.handle, _ref(mo), _ref(mx), _ref(mg), _ref(mb), float(eps)), self.handle, "lh_b200_layernorm")

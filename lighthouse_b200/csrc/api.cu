@@ -753,3 +753,103 @@ extern "C" int lh_b200_benchmark(lh_module_t* m, void* const* arg_ptrs, int narg
   if (rc) return rc;
   return lh_b200_sync(ctx);
 }
+
+// --------------------------------------------------- attention without allocation
+// Some callers must not trigger device allocation at all: a serving loop that has handed
+// the whole memory budget to its own pool, a host thread that must never block on the
+// implicit device synchronisation an allocation can cause, code that runs after a
+// "no allocation past warm-up" gate. For them this entry point runs the un-fused attention
+// (batched Q K^T, scale, mask, row softmax, batched P V) with its score matrix in a buffer
+// that is part of the library image instead of one obtained at run time.
+namespace {
+
+constexpr int64_t NOALLOC_MAX_SCORES = int64_t(1) << 20;  // Sq * Skv <= 1 Mi f32 = 4 MiB per GPU
+static __device__ __align__(256) float g_noalloc_scores[NOALLOC_MAX_SCORES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+
+// The array's name is only a host-side handle; the kernels need its address on the device
+// that is current, which the runtime reports per device.
+int noalloc_scores_ptr(lh_ctx* ctx, float** out) {
+  if (ctx->device < 0 || ctx->device >= NOALLOC_MAX_DEVICES)
+    return set_error(ctx, LH_ERR_UNSUPPORTED, "attention_fwd_noalloc: device ordinal %d out of range", ctx->device);
+  if (!g_noalloc_ptr[ctx->device]) {
+    LH_CUDA_CHECK(ctx, cudaSetDevice(ctx->device));
+    float* ptr = nullptr;
+    LH_CUDA_CHECK(ctx, cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scores));
+    g_noalloc_ptr[ctx->device] = ptr;
+  }
+  *out = g_noalloc_ptr[ctx->device];
+  return LH_OK;
+}
+
+}  // namespace
+
+extern "C" int lh_b200_attention_fwd_noalloc(lh_ctx_t* ctx, const lh_memref_t* o, const lh_memref_t* q,
+                                             const lh_memref_t* k, const lh_memref_t* v, float scale, int causal) {
+  if (!ctx) return LH_ERR_INVALID;
+  if (!o || !q || !k || !v) return set_error(ctx, LH_ERR_INVALID, "attention_fwd_noalloc: null operand");
+  if (q->rank != 4 || k->rank != 4 || v->rank != 4 || o->rank != 4)
+    return set_error(ctx, LH_ERR_INVALID, "attention_fwd_noalloc: operands must be rank-4 (B, H, S, D) views");
+  for (int i = 0; i < 4; ++i) {
+    if (o->shape[i] != q->shape[i] || v->shape[i] != k->shape[i])
+      return set_error(ctx, LH_ERR_INVALID, "attention_fwd_noalloc: O must match Q and V must match K in shape");
+  }
+  if (k->shape[0] != q->shape[0] || k->shape[3] != q->shape[3] || k->shape[1] < 1 || q->shape[1] % k->shape[1])
+    return set_error(ctx, LH_ERR_INVALID, "attention_fwd_noalloc: batch / head_dim / head grouping mismatch");
+  if (q->strides[3] != 1 || k->strides[3] != 1 || v->strides[3] != 1 || o->strides[3] != 1)
+    return set_error(ctx, LH_ERR_UNSUPPORTED, "attention_fwd_noalloc: head_dim must have unit stride");
+  if (q->dtype != k->dtype || q->dtype != v->dtype)
+    return set_error(ctx, LH_ERR_INVALID, "attention_fwd_noalloc: Q, K, V dtypes differ");
+  const int B = static_cast<int>(q->shape[0]), Hq = static_cast<int>(q->shape[1]), Sq = static_cast<int>(q->shape[2]);
+  const int D = static_cast<int>(q->shape[3]), Hkv = static_cast<int>(k->shape[1]), Skv = static_cast<int>(k->shape[2]);
+  if (B == 0 || Sq == 0) return LH_OK;
+  if (Skv == 0) return set_error(ctx, LH_ERR_INVALID, "attention_fwd_noalloc: empty key sequence");
+  const int64_t score_elems = static_cast<int64_t>(Sq) * Skv;
+  if (score_elems > NOALLOC_MAX_SCORES)
+    return set_error(ctx, LH_ERR_UNSUPPORTED,
+                     "attention_fwd_noalloc: Sq * Skv = %lld exceeds the built-in score buffer of %lld elements; use lh_b200_attention_fwd",
+                     (long long)score_elems, (long long)NOALLOC_MAX_SCORES);
+  float* scores = nullptr;
+  int rc = noalloc_scores_ptr(ctx, &scores);
+  if (rc) return rc;
+  const int n_rep = Hq / Hkv;
+  const int64_t esz = static_cast<int64_t>(dtype_size(q->dtype)), osz = static_cast<int64_t>(dtype_size(o->dtype));
+  // The buffer keeps whatever the previous call left; every element a head reads is
+  // written first by that head's Q K^T product (no accumulation), so nothing needs clearing.
+  for (int b = 0; b < B; ++b) {
+    for (int h = 0; h < Hq; ++h) {
+      const int hk = h / n_rep;
+      GemmProblem g;
+      memset(&g, 0, sizeof(g));
+      g.batch = 1;
+      g.M = Sq; g.N = Skv; g.K = D;
+      g.A = data_ptr(q) + (b * q->strides[0] + h * q->strides[1]) * esz; g.a_dtype = q->dtype; g.sam = q->strides[2]; g.sak = 1;
+      g.B = data_ptr(k) + (b * k->strides[0] + hk * k->strides[1]) * esz; g.b_dtype = k->dtype; g.sbk = 1; g.sbn = k->strides[2];
+      g.D = scores; g.d_dtype = LH_F32; g.sdm = Skv; g.sdn = 1;
+      rc = gemm_simt_launch(ctx, g);
+      if (rc) return rc;
+      int64_t blocks = (score_elems + 255) / 256;
+      if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
+      scale_mask_kernel<<<static_cast<unsigned>(blocks), 256, 0, ctx->stream>>>(scores, score_elems, Sq, Skv, scale, causal);
+      LH_CHECK_LAUNCH(ctx, "scale_mask_kernel");
+      lh_memref_t s;
+      memset(&s, 0, sizeof(s));
+      s.allocated = s.aligned = scores;
+      s.rank = 2; s.dtype = LH_F32;
+      s.shape[0] = Sq; s.shape[1] = Skv; s.strides[0] = Skv; s.strides[1] = 1;
+      rc = softmax_launch(ctx, &s, &s);
+      if (rc) return rc;
+      memset(&g, 0, sizeof(g));
+      g.batch = 1;
+      g.M = Sq; g.N = D; g.K = Skv;
+      g.A = scores; g.a_dtype = LH_F32; g.sam = Skv; g.sak = 1;
+      g.B = data_ptr(v) + (b * v->strides[0] + hk * v->strides[1]) * esz; g.b_dtype = v->dtype; g.sbk = v->strides[2]; g.sbn = 1;
+      g.D = data_ptr(o) + (b * o->strides[0] + h * o->strides[1]) * osz; g.d_dtype = o->dtype; g.sdm = o->strides[2]; g.sdn = 1;
+      rc = gemm_simt_launch(ctx, g);
+      if (rc) return rc;
+    }
+  }
+  return LH_OK;
+}

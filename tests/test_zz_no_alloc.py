@@ -1,0 +1,73 @@
+"""``lh_b200_attention_fwd_noalloc`` — attention for callers that may not allocate.
+
+Some users of this library run where a device allocation is off the table: the process has
+given all free memory to its own pool, or a request loop promises not to allocate once it is
+warm, or the calling thread cannot afford the device-wide stall an allocation can bring. The
+ordinary un-fused attention path gets its score scratch from ``cudaMalloc``; this entry point
+keeps the scores in a 4 MiB buffer that ships inside the library instead.
+
+The test calls it through the C ABI twice in a row (the buffer still holds the first call's
+scores when the second one starts) and checks both results against the existing entry point,
+``lh_b200_attention_fwd``, on the same f32 inputs (which also takes the un-fused route).
+The file name makes pytest collect it last, so a run that stops at the first failure has
+already been through every other test.
+"""
+
+import ctypes
+
+import pytest
+import torch
+
+from lighthouse_b200 import _native as N
+from lighthouse_b200.context import as_memref
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-5  # same bound the other f32 parity tests use
+
+
+def rel_err(a, b):
+    return float((a - b).abs().max() / (b.abs().max() + 1e-30))
+
+
+def call_noalloc(ctx, o, q, k, v, scale, causal):
+    mo, mq, mk, mv = (as_memref(t) for t in (o, q, k, v))
+    return ctx._lib.lh_b200_attention_fwd_noalloc(ctx.handle, ctypes.byref(mo), ctypes.byref(mq), ctypes.byref(mk), ctypes.byref(mv), float(scale), int(causal))
+
+
+def test_noalloc_attention_matches_existing_entry_point_twice(ctx):
+    g = torch.Generator().manual_seed(21)
+    shapes = [((2, 4, 96, 32), (2, 2, 160, 32), True), ((1, 3, 200, 64), (1, 3, 200, 64), False)]
+    for (qs, ks, causal) in shapes:  # two calls in a row, second one on a dirty buffer
+        q = torch.randn(*qs, generator=g).cuda()
+        k = torch.randn(*ks, generator=g).cuda()
+        v = torch.randn(*ks, generator=g).cuda()
+        scale = qs[-1] ** -0.5
+        want = torch.empty_like(q)
+        ctx.attention_fwd(want, q, k, v, scale, causal)
+        ctx.sync()
+        got = torch.full_like(q, float("nan"))
+        rc = call_noalloc(ctx, got, q, k, v, scale, causal)
+        assert rc == N.LH_OK, ctx._lib.lh_b200_last_error(ctx.handle)
+        ctx.sync()
+        assert rel_err(got, want) <= TOL_F32
+    # bf16 inputs work too (compared with the same op sequence on the existing path is not
+    # possible there — bf16 goes to the fused kernel — so compare against the f32 result)
+    qb, kb, vb = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    ref = torch.empty_like(q)
+    ctx.attention_fwd(ref, qb.float(), kb.float(), vb.float(), scale, causal)
+    out = torch.empty_like(qb)
+    assert call_noalloc(ctx, out, qb, kb, vb, scale, causal) == N.LH_OK
+    ctx.sync()
+    assert rel_err(out.float(), ref) <= 2e-2
+
+
+def test_noalloc_attention_rejects_sizes_beyond_its_buffer(ctx):
+    q = torch.zeros(1, 1, 2048, 16, device="cuda")
+    o = torch.empty_like(q)
+    rc = call_noalloc(ctx, o, q, q, q, 0.25, False)  # 2048 * 2048 scores > 1 Mi
+    assert rc == N.LH_ERR_UNSUPPORTED
+    msg = ctx._lib.lh_b200_last_error(ctx.handle).decode()
+    assert "exceeds" in msg and "1048576" in msg
+    bad = torch.zeros(1, 2, 8, 16, device="cuda")
+    assert call_noalloc(ctx, o, q, bad, bad, 0.25, False) != N.LH_OK  # 1 query head, 2 kv heads
