@@ -411,6 +411,10 @@ int attn_tc_supported(const lh_ctx* ctx, const AttnProblem& a) {
 }
 
 int attn_tc_launch(lh_ctx* ctx, const AttnProblem& a) {
+  // Default: the kernel that keeps P in tensor memory (attention_tc2.cu). This file's kernel
+  // (P through shared memory, one CTA per SM) stays selectable for comparison.
+  const char* v1 = getenv("LH_B200_ATTN_V1");
+  if (!(v1 && v1[0] == '1') && a.scale > 0.f) return attn_tc2_launch(ctx, a);
   if (a.D == 128) return launch_hd<128>(ctx, a);
   return launch_hd<64>(ctx, a);
 }
