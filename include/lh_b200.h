@@ -226,8 +226,30 @@ int lh_b200_comm_init(lh_ctx_t* ctx, const char* nccl_path, const void* id128, i
 int lh_b200_comm_destroy(lh_ctx_t* ctx);
 /* In-place sum all-reduce of the (contiguous) view on the context stream. */
 int lh_b200_allreduce(lh_ctx_t* ctx, const lh_memref_t* buf);
+/* out (n) = this rank's block of the element-wise sum over ranks of in (world * n); both
+ * contiguous. Together with lh_b200_allgather it splits the all-reduce in two, so that the
+ * work between them (residual add, normalisation) runs on 1/world of the rows. */
+int lh_b200_reducescatter(lh_ctx_t* ctx, const lh_memref_t* out, const lh_memref_t* in);
 /* out (world * n) = concatenation over ranks of in (n), contiguous. */
 int lh_b200_allgather(lh_ctx_t* ctx, const lh_memref_t* out, const lh_memref_t* in);
+
+/* ----------------------------------------------------- side stream / events */
+/*
+ * A context owns a second, high-priority stream for work that should overlap the main
+ * stream (a collective and the small kernels around it, while the GEMMs of another
+ * micro-batch run). lh_b200_stream_select(ctx, 1) routes every following call of this
+ * library to the side stream, (ctx, 0) back to the main one. Ordering between the two is
+ * by numbered events: lh_b200_event_record marks the selected stream's position,
+ * lh_b200_event_wait makes the selected stream wait for the last record of that number.
+ * lh_b200_sync waits for both streams. lh_b200_reserve_sms(ctx, n) makes persistent kernels
+ * (the tcgen05 GEMM) launch sm_count - n blocks, so that side-stream kernels find free SMs
+ * while a GEMM runs; 0 restores the full grid. The reference has no counterpart: its MPI
+ * example communicates synchronously (examples/mpi/feed-forward-mpi.py:213-228).
+ */
+int lh_b200_stream_select(lh_ctx_t* ctx, int side);
+int lh_b200_event_record(lh_ctx_t* ctx, int id);
+int lh_b200_event_wait(lh_ctx_t* ctx, int id);
+int lh_b200_reserve_sms(lh_ctx_t* ctx, int n);
 
 /* ------------------------------------------------------------------ modules */
 /*
@@ -247,7 +269,12 @@ typedef enum {
   LH_OP_ELEMENTWISE = 7,
   LH_OP_EMBEDDING = 8,
   LH_OP_ALLREDUCE = 9,
-  LH_OP_ALLGATHER = 10
+  LH_OP_ALLGATHER = 10,
+  LH_OP_REDUCESCATTER = 11,
+  LH_OP_STREAM = 12,
+  LH_OP_EVENT_RECORD = 13,
+  LH_OP_EVENT_WAIT = 14,
+  LH_OP_RESERVE_SMS = 15
 } lh_op_kind_t;
 
 /* An operand: a view into a slot. slot < 0 means "absent". */
@@ -273,6 +300,10 @@ typedef struct {
  *   EMBEDDING   out, ids, wte, wpe              i0 = period
  *   ALLREDUCE   buf
  *   ALLGATHER   out, in
+ *   REDUCESCATTER out, in
+ *   STREAM      (none)                          i0 = 0 main / 1 side
+ *   EVENT_RECORD, EVENT_WAIT (none)             i0 = event number
+ *   RESERVE_SMS (none)                          i0 = SMs left free by persistent kernels
  */
 typedef struct {
   int32_t kind;
@@ -320,6 +351,9 @@ int lh_b200_benchmark(lh_module_t* m, void* const* arg_ptrs, int nargs, double* 
  * fills ms[i] with operator i's duration in milliseconds (n = number of operators). */
 int lh_b200_module_set_profiling(lh_module_t* m, int enable);
 int lh_b200_module_op_times(lh_module_t* m, float* ms, int n);
+/* The same events read as a timeline: ms[i] = when operator i ended, measured from the start
+ * of the run. With operators on two streams this shows what overlapped what. */
+int lh_b200_module_op_end_times(lh_module_t* m, float* ms, int n);
 /* Captures one module_run into a CUDA graph and replays it on later runs. */
 int lh_b200_module_use_graph(lh_module_t* m, int enable);
 

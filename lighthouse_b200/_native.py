@@ -67,7 +67,12 @@ EW_COPY, EW_ADD, EW_MUL, EW_ACT, EW_ADD_ACT, EW_SILU_MUL, EW_SCALE, EW_FILL, EW_
     OP_EMBEDDING,
     OP_ALLREDUCE,
     OP_ALLGATHER,
-) = range(1, 11)
+    OP_REDUCESCATTER,
+    OP_STREAM,
+    OP_EVENT_RECORD,
+    OP_EVENT_WAIT,
+    OP_RESERVE_SMS,
+) = range(1, 16)
 
 
 class MemRef(Structure):
@@ -150,6 +155,11 @@ _PROTOTYPES = {
     "lh_b200_comm_init": (c_int, [c_void_p, c_char_p, c_void_p, c_int, c_int]),
     "lh_b200_comm_destroy": (c_int, [c_void_p]),
     "lh_b200_allreduce": (c_int, [c_void_p, POINTER(MemRef)]),
+    "lh_b200_reducescatter": (c_int, [c_void_p, POINTER(MemRef), POINTER(MemRef)]),
+    "lh_b200_stream_select": (c_int, [c_void_p, c_int]),
+    "lh_b200_event_record": (c_int, [c_void_p, c_int]),
+    "lh_b200_event_wait": (c_int, [c_void_p, c_int]),
+    "lh_b200_reserve_sms": (c_int, [c_void_p, c_int]),
     "lh_b200_allgather": (c_int, [c_void_p, POINTER(MemRef), POINTER(MemRef)]),
     "lh_b200_module_create": (
         c_int,
@@ -175,6 +185,7 @@ _PROTOTYPES = {
     "lh_b200_module_use_graph": (c_int, [c_void_p, c_int]),
     "lh_b200_module_set_profiling": (c_int, [c_void_p, c_int]),
     "lh_b200_module_op_times": (c_int, [c_void_p, POINTER(c_float), c_int]),
+    "lh_b200_module_op_end_times": (c_int, [c_void_p, POINTER(c_float), c_int]),
 }
 
 EXPORTED_SYMBOLS = tuple(_PROTOTYPES)

@@ -193,6 +193,12 @@ extern "C" int lh_b200_ctx_destroy(lh_ctx_t* ctx) {
     cudaStreamSynchronize(ctx->own_stream);
     cudaStreamDestroy(ctx->own_stream);
   }
+  if (ctx->side_stream) {
+    cudaStreamSynchronize(ctx->side_stream);
+    cudaStreamDestroy(ctx->side_stream);
+  }
+  for (cudaEvent_t e : ctx->events)
+    if (e) cudaEventDestroy(e);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
   if (ctx->host_status) cudaFreeHost(ctx->host_status);
@@ -202,6 +208,7 @@ extern "C" int lh_b200_ctx_destroy(lh_ctx_t* ctx) {
 
 extern "C" int lh_b200_ctx_set_stream(lh_ctx_t* ctx, void* cuda_stream, int use_external) {
   if (!ctx) return LH_ERR_INVALID;
+  if (ctx->side_selected) return set_error(ctx, LH_ERR_INVALID, "ctx_set_stream while the side stream is selected");
   ctx->stream = use_external ? static_cast<cudaStream_t>(cuda_stream) : ctx->own_stream;
   return LH_OK;
 }
@@ -210,6 +217,8 @@ extern "C" void* lh_b200_ctx_get_stream(lh_ctx_t* ctx) { return ctx ? ctx->strea
 
 extern "C" int lh_b200_sync(lh_ctx_t* ctx) {
   if (!ctx) return LH_ERR_INVALID;
+  if (ctx->side_selected) lh_b200_stream_select(ctx, 0);
+  if (ctx->side_stream) LH_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->side_stream));
   LH_CUDA_CHECK(ctx, cudaMemcpyAsync(ctx->host_status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
   LH_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
   const int st = *ctx->host_status;
@@ -422,6 +431,7 @@ typedef int (*nccl_init_rank_t)(void**, int, NcclId, int);
 typedef int (*nccl_destroy_t)(void*);
 typedef int (*nccl_allreduce_t)(const void*, void*, size_t, int, int, void*, cudaStream_t);
 typedef int (*nccl_allgather_t)(const void*, void*, size_t, int, void*, cudaStream_t);
+typedef int (*nccl_reducescatter_t)(const void*, void*, size_t, int, int, void*, cudaStream_t);
 typedef const char* (*nccl_errstr_t)(int);
 
 void* open_nccl(const char* path) {
@@ -503,12 +513,87 @@ extern "C" int lh_b200_allreduce(lh_ctx_t* ctx, const lh_memref_t* buf) {
   return LH_OK;
 }
 
+extern "C" int lh_b200_reducescatter(lh_ctx_t* ctx, const lh_memref_t* out, const lh_memref_t* in) {
+  if (!ctx || !out || !in) return LH_ERR_INVALID;
+  if (!is_contiguous(out) || !is_contiguous(in)) return set_error(ctx, LH_ERR_UNSUPPORTED, "reducescatter: buffers must be contiguous");
+  if (out->dtype != in->dtype || numel(in) != numel(out) * ctx->world) return set_error(ctx, LH_ERR_INVALID, "reducescatter: size mismatch");
+  if (ctx->world == 1 && !ctx->nccl_comm) {
+    if (data_ptr(out) == data_ptr(in)) return LH_OK;
+    return lh_b200_memcpy(ctx, data_ptr(out), data_ptr(in), static_cast<size_t>(numel(in)) * dtype_size(in->dtype), 2);
+  }
+  if (!ctx->nccl_comm) return set_error(ctx, LH_ERR_COMM, "reducescatter: communicator not initialised");
+  const int dt = nccl_dtype(in->dtype);
+  auto fn = reinterpret_cast<nccl_reducescatter_t>(dlsym(ctx->nccl_lib, "ncclReduceScatter"));
+  if (!fn || dt < 0) return set_error(ctx, LH_ERR_COMM, "ncclReduceScatter unavailable");
+  int r = fn(data_ptr(in), data_ptr(out), static_cast<size_t>(numel(out)), dt, /*ncclSum*/ 0, ctx->nccl_comm, ctx->stream);
+  if (r != 0) return set_error(ctx, LH_ERR_COMM, "ncclReduceScatter failed (%d)", r);
+  return LH_OK;
+}
+
+// ------------------------------------------------------- side stream / events
+extern "C" int lh_b200_stream_select(lh_ctx_t* ctx, int side) {
+  if (!ctx) return LH_ERR_INVALID;
+  if ((side != 0) == ctx->side_selected) return LH_OK;
+  if (side) {
+    if (!ctx->side_stream) {
+      int least = 0, greatest = 0;
+      LH_CUDA_CHECK(ctx, cudaDeviceGetStreamPriorityRange(&least, &greatest));
+      LH_CUDA_CHECK(ctx, cudaStreamCreateWithPriority(&ctx->side_stream, cudaStreamNonBlocking, greatest));
+    }
+    ctx->main_saved = ctx->stream;
+    ctx->stream = ctx->side_stream;
+    ctx->side_selected = true;
+  } else {
+    ctx->stream = ctx->main_saved;
+    ctx->side_selected = false;
+  }
+  return LH_OK;
+}
+
+static int numbered_event(lh_ctx* ctx, int id, bool create, cudaEvent_t* out) {
+  if (id < 0 || id >= 4096) return set_error(ctx, LH_ERR_INVALID, "event number %d out of range [0, 4096)", id);
+  if (static_cast<size_t>(id) >= ctx->events.size()) ctx->events.resize(id + 1, nullptr);
+  if (!ctx->events[id]) {
+    if (!create) return set_error(ctx, LH_ERR_INVALID, "event %d waited for before any record", id);
+    LH_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->events[id], cudaEventDisableTiming));
+  }
+  *out = ctx->events[id];
+  return LH_OK;
+}
+
+extern "C" int lh_b200_event_record(lh_ctx_t* ctx, int id) {
+  if (!ctx) return LH_ERR_INVALID;
+  cudaEvent_t e;
+  int rc = numbered_event(ctx, id, true, &e);
+  if (rc) return rc;
+  LH_CUDA_CHECK(ctx, cudaEventRecord(e, ctx->stream));
+  return LH_OK;
+}
+
+extern "C" int lh_b200_event_wait(lh_ctx_t* ctx, int id) {
+  if (!ctx) return LH_ERR_INVALID;
+  cudaEvent_t e;
+  int rc = numbered_event(ctx, id, false, &e);
+  if (rc) return rc;
+  LH_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->stream, e, 0));
+  return LH_OK;
+}
+
+extern "C" int lh_b200_reserve_sms(lh_ctx_t* ctx, int n) {
+  if (!ctx) return LH_ERR_INVALID;
+  if (n < 0 || n >= ctx->sm_count) return set_error(ctx, LH_ERR_INVALID, "reserve_sms: %d of %d SMs", n, ctx->sm_count);
+  ctx->reserved_sms = n;
+  return LH_OK;
+}
+
 extern "C" int lh_b200_allgather(lh_ctx_t* ctx, const lh_memref_t* out, const lh_memref_t* in) {
   if (!ctx || !out || !in) return LH_ERR_INVALID;
   if (!is_contiguous(out) || !is_contiguous(in)) return set_error(ctx, LH_ERR_UNSUPPORTED, "allgather: buffers must be contiguous");
   if (out->dtype != in->dtype || numel(out) != numel(in) * ctx->world) return set_error(ctx, LH_ERR_INVALID, "allgather: size mismatch");
-  if (ctx->world == 1 && !ctx->nccl_comm)
+  if (ctx->world == 1 && !ctx->nccl_comm) {
+    if (data_ptr(out) == data_ptr(in)) return LH_OK;
     return lh_b200_memcpy(ctx, data_ptr(out), data_ptr(in), static_cast<size_t>(numel(in)) * dtype_size(in->dtype), 2);
+  }
   if (!ctx->nccl_comm) return set_error(ctx, LH_ERR_COMM, "allgather: communicator not initialised");
   const int dt = nccl_dtype(in->dtype);
   auto fn = reinterpret_cast<nccl_allgather_t>(dlsym(ctx->nccl_lib, "ncclAllGather"));
@@ -542,7 +627,7 @@ extern "C" int lh_b200_module_create(lh_ctx_t* ctx, const char* entry_name, cons
   *out = nullptr;
   const int nslots = nargs + ntemps;
   for (int i = 0; i < nops; ++i) {
-    if (ops[i].kind < LH_OP_GEMM || ops[i].kind > LH_OP_ALLGATHER) return set_error(ctx, LH_ERR_INVALID, "module_create: op %d has unknown kind %d", i, ops[i].kind);
+    if (ops[i].kind < LH_OP_GEMM || ops[i].kind > LH_OP_RESERVE_SMS) return set_error(ctx, LH_ERR_INVALID, "module_create: op %d has unknown kind %d", i, ops[i].kind);
     for (int j = 0; j < LH_MAX_OPERANDS; ++j) {
       const lh_view_t& v = ops[i].operands[j];
       if (v.slot >= nslots) return set_error(ctx, LH_ERR_INVALID, "module_create: op %d operand %d names slot %d of %d", i, j, v.slot, nslots);
@@ -613,15 +698,27 @@ static int run_ops(lh_module* m, void* const* arg_ptrs) {
       case LH_OP_ELEMENTWISE: rc = lh_b200_elementwise(ctx, op.i0, o[0], o[1], o[2], op.i1, op.f0); break;
       case LH_OP_EMBEDDING: rc = lh_b200_embedding(ctx, o[0], o[1], o[2], o[3], op.i0); break;
       case LH_OP_ALLREDUCE: rc = lh_b200_allreduce(ctx, o[0]); break;
+      case LH_OP_REDUCESCATTER: rc = lh_b200_reducescatter(ctx, o[0], o[1]); break;
+      case LH_OP_STREAM: rc = lh_b200_stream_select(ctx, op.i0); break;
+      case LH_OP_EVENT_RECORD: rc = lh_b200_event_record(ctx, op.i0); break;
+      case LH_OP_EVENT_WAIT: rc = lh_b200_event_wait(ctx, op.i0); break;
+      case LH_OP_RESERVE_SMS: rc = lh_b200_reserve_sms(ctx, op.i0); break;
       case LH_OP_ALLGATHER: rc = lh_b200_allgather(ctx, o[0], o[1]); break;
       default: rc = set_error(ctx, LH_ERR_INVALID, "unknown op kind %d", op.kind);
     }
     if (rc) {
       char msg[400];
       snprintf(msg, sizeof(msg), "%s", ctx->err);
+      lh_b200_stream_select(ctx, 0);
+      ctx->reserved_sms = 0;
       return set_error(ctx, rc, "op %zu (kind %d): %s", i, op.kind, msg);
     }
     if (m->profiling) cudaEventRecord(m->op_events[i + 1], ctx->stream);
+  }
+  if (ctx->side_selected || ctx->reserved_sms) {
+    lh_b200_stream_select(ctx, 0);
+    ctx->reserved_sms = 0;
+    return set_error(ctx, LH_ERR_INVALID, "module '%s' ends with the side stream selected or SMs reserved", m->entry.c_str());
   }
   return LH_OK;
 }
@@ -685,8 +782,23 @@ extern "C" int lh_b200_module_op_times(lh_module_t* m, float* ms, int n) {
   return LH_OK;
 }
 
+extern "C" int lh_b200_module_op_end_times(lh_module_t* m, float* ms, int n) {
+  if (!m || !ms) return LH_ERR_INVALID;
+  lh_ctx* ctx = m->ctx;
+  if (m->op_events.empty() || n != static_cast<int>(m->ops.size()))
+    return set_error(ctx, LH_ERR_INVALID, "op_end_times: profiling was not enabled or n != number of operators");
+  for (int i = 0; i < n; ++i) {
+    LH_CUDA_CHECK(ctx, cudaEventSynchronize(m->op_events[i + 1]));
+    LH_CUDA_CHECK(ctx, cudaEventElapsedTime(&ms[i], m->op_events[0], m->op_events[i + 1]));
+  }
+  return LH_OK;
+}
+
 extern "C" int lh_b200_module_use_graph(lh_module_t* m, int enable) {
   if (!m) return LH_ERR_INVALID;
+  if (enable)
+    for (const lh_op_t& op : m->ops)
+      if (op.kind == LH_OP_STREAM) return set_error(m->ctx, LH_ERR_UNSUPPORTED, "graph mode is not available for modules that use the side stream");
   m->use_graph = enable != 0;
   return LH_OK;
 }

@@ -11,6 +11,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <vector>
+
 #include "../../include/lh_b200.h"
 
 struct lh_ctx {
@@ -32,6 +34,12 @@ struct lh_ctx {
   void* nccl_lib = nullptr;
   void* nccl_comm = nullptr;
   int rank = 0, world = 1;
+  // side stream (collectives overlapping the main stream) and the numbered events ordering the two
+  cudaStream_t side_stream = nullptr;
+  cudaStream_t main_saved = nullptr;  // the main stream while the side stream is selected
+  bool side_selected = false;
+  std::vector<cudaEvent_t> events;    // indexed by event number, created on first use
+  int reserved_sms = 0;               // SMs persistent kernels leave free
 };
 
 namespace lh {

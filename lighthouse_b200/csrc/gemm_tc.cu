@@ -438,7 +438,10 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi) {
   auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES, OUT_F32>;
   LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
-  const int grid = num_tiles < ctx->sm_count ? num_tiles : ctx->sm_count;
+  // A persistent grid that fills the GPU would make side-stream kernels (collectives) wait for
+  // this kernel's end; lh_b200_reserve_sms leaves them room.
+  const int sms = ctx->sm_count - ctx->reserved_sms > 0 ? ctx->sm_count - ctx->reserved_sms : 1;
+  const int grid = num_tiles < sms ? num_tiles : sms;
   kernel<<<grid, NUM_THREADS, L::DYN_BYTES, ctx->stream>>>(tmA, tmB, tmD, p);
   LH_CHECK_LAUNCH(ctx, "gemm_bf16_tc_kernel");
   return LH_OK;

@@ -146,7 +146,7 @@ class PView:
 
 @dataclass
 class PlanOp:
-    kind: str  # gemm | attention | layernorm | rmsnorm | softmax | rope | elementwise | embedding | allreduce | allgather
+    kind: str  # one of the keys of _KIND_CODES below
     operands: list  # PView | None, in the order lh_b200.h documents
     attrs: dict = field(default_factory=dict)
 
@@ -175,6 +175,11 @@ _KIND_CODES = {
     "embedding": N.OP_EMBEDDING,
     "allreduce": N.OP_ALLREDUCE,
     "allgather": N.OP_ALLGATHER,
+    "reducescatter": N.OP_REDUCESCATTER,
+    "stream": N.OP_STREAM,
+    "event_record": N.OP_EVENT_RECORD,
+    "event_wait": N.OP_EVENT_WAIT,
+    "reserve_sms": N.OP_RESERVE_SMS,
 }
 
 
@@ -240,8 +245,29 @@ class Plan:
         return out
 
     def allreduce(self, buf):
+        """Sum over the tensor-parallel ranks, in place."""
         self.ops.append(PlanOp("allreduce", [buf]))
         return buf
+
+    def reducescatter(self, out, inp):
+        """``out`` = this rank's block of the sum over ranks of ``inp`` (world blocks)."""
+        self.ops.append(PlanOp("reducescatter", [out, inp]))
+        return out
+
+    # -- side stream: operators after ``stream(1)`` go to the context's second stream until
+    # ``stream(0)``; numbered events order the two streams.
+    def stream(self, side: int):
+        self.ops.append(PlanOp("stream", [], {"index": int(side)}))
+
+    def event_record(self, number: int):
+        self.ops.append(PlanOp("event_record", [], {"index": int(number)}))
+
+    def event_wait(self, number: int):
+        self.ops.append(PlanOp("event_wait", [], {"index": int(number)}))
+
+    def reserve_sms(self, n: int):
+        """Persistent GEMMs leave ``n`` SMs to side-stream kernels from here on (0: none)."""
+        self.ops.append(PlanOp("reserve_sms", [], {"index": int(n)}))
 
     def allgather(self, out, inp):
         self.ops.append(PlanOp("allgather", [out, inp]))
@@ -286,6 +312,8 @@ class Plan:
                 o.i0, o.i1, o.f0 = EW_CODES[at["ew"]], ACT_CODES[at.get("act", "none")], at.get("scalar", 0.0)
             elif op.kind == "embedding":
                 o.i0 = at.get("period", 0)
+            elif op.kind in ("stream", "event_record", "event_wait", "reserve_sms"):
+                o.i0 = at["index"]
         return sig, nargs, temps, len(self.temp_bytes), ops, len(self.ops)
 
     def __str__(self) -> str:

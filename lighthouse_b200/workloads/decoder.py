@@ -269,6 +269,128 @@ def build_llama_plan(cfg: LlamaConfig, rank: int = 0, tp: int = 1, name: str = "
     return p
 
 
+class _SideChain:
+    """Bookkeeping for plans that overlap collectives with compute: each micro-batch's
+    contracting GEMM on the main stream is followed, on the side stream, by reduce-scatter ->
+    residual add -> norm on this rank's rows -> all-gather, while the main stream runs the
+    other micro-batch. ``ready[mb]`` is the event after which ``xn[mb]`` holds the gathered,
+    normalised activations."""
+
+    def __init__(self, p: Plan, microbatches: int):
+        self.p = p
+        self.next_event = 0
+        self.ready = [None] * microbatches
+
+    def event(self) -> int:
+        self.next_event += 1
+        return self.next_event - 1
+
+    def fork(self) -> None:
+        """Side stream continues from the main stream's current position."""
+        e = self.event()
+        self.p.event_record(e)
+        self.p.stream(1)
+        self.p.event_wait(e)
+
+    def join(self, mb: int) -> None:
+        """Back to the main stream; ``ready[mb]`` marks the side chain's end."""
+        self.ready[mb] = self.event()
+        self.p.event_record(self.ready[mb])
+        self.p.stream(0)
+
+
+def check_overlap(tokens: int, batch: int, tp: int, microbatches: int) -> None:
+    if microbatches < 1 or batch % microbatches:
+        raise ValueError(f"batch {batch} does not split into {microbatches} micro-batches of whole sequences")
+    if (tokens // microbatches) % tp:
+        raise ValueError(f"{tokens // microbatches} tokens per micro-batch do not split into {tp} row blocks")
+
+
+def build_llama_plan_overlapped(cfg: LlamaConfig, rank: int, tp: int, microbatches: int = 2, reserve_sms: int = 16,
+                                name: str = "llama_forward") -> Plan:
+    """Same arguments and result as ``build_llama_plan``; different schedule for ``tp`` > 1.
+
+    The all-reduce after each contraction is split into reduce-scatter + all-gather with the
+    residual stream sharded by rows between them (each rank adds the residual and normalises
+    1/tp of the tokens instead of all of them), and the batch is cut into micro-batches of
+    whole sequences so that one micro-batch's collectives run on the side stream under the
+    other's GEMMs and attention. Only the last collective of the step is exposed."""
+    check_tp(cfg, tp)
+    check_overlap(cfg.tokens, cfg.batch, tp, microbatches)
+    d, t, hd = cfg.dim, cfg.tokens, cfg.head_dim
+    hq, hkv, fl = cfg.n_heads // tp, cfg.n_kv_heads // tp, cfg.ffn // tp
+    ql, kl = hq * hd, hkv * hd
+    width = ql + 2 * kl
+    args = [ArgSpec((t, d), "bf16", "out"), ArgSpec((t, d), "bf16", "x")]
+    per_layer = [((d,), "bf16"), ((width, d), "bf16"), ((d, ql), "bf16"), ((d,), "bf16"), ((2 * fl, d), "bf16"), ((d, fl), "bf16")]
+    for li in range(cfg.n_layer):
+        args += [ArgSpec(s, dt, f"l{li}.{k}") for (s, dt), k in zip(per_layer, LLAMA_LAYER_KEYS)]
+    args.append(ArgSpec((d,), "bf16", "norm"))
+    p = Plan(name, args)
+    m = microbatches
+    bm, tm = cfg.batch // m, t // m
+    ts = tm // tp
+    h = [p.temp((ts, d), "bf16") for _ in range(m)]       # this rank's rows of the residual stream
+    xn = [p.temp((tm, d), "bf16") for _ in range(m)]      # gathered normalised activations
+    qkv = [p.temp((tm, width), "bf16") for _ in range(m)]
+    att = [p.temp((tm, ql), "bf16") for _ in range(m)]
+    ff = [p.temp((tm, fl), "bf16") for _ in range(m)]
+    part = [p.temp((tm, d), "bf16") for _ in range(m)]    # this rank's partial sums of a contraction
+    rs = [p.temp((ts, d), "bf16") for _ in range(m)]
+    chain = _SideChain(p, m)
+    layer_args = lambda li: {k: p.arg(2 + li * len(LLAMA_LAYER_KEYS) + i) for i, k in enumerate(LLAMA_LAYER_KEYS)}
+    final_norm = p.arg(len(args) - 1)
+
+    def bshd(view2d: PView, col0: int, nheads: int) -> PView:
+        v = view2d.slice(1, col0, nheads * hd)
+        return PView(v.slot, (bm, cfg.seq, nheads, hd), (cfg.seq * v.strides[0], v.strides[0], hd, 1), v.dtype, v.offset)
+
+    def norm_and_gather(mb: int, weight: PView, last: bool) -> None:
+        """On the side stream: normalise this rank's rows into their place in the gathered
+        buffer (the result argument itself after the last layer) and all-gather in place."""
+        full = p.arg(0).slice(0, mb * tm, tm) if last else xn[mb]
+        mine = full.slice(0, rank * ts, ts)
+        p.rmsnorm(mine, h[mb], weight, cfg.eps)
+        p.allgather(full, mine)
+
+    p.reserve_sms(reserve_sms)
+    for mb in range(m):
+        chain.fork()
+        p.elementwise("copy", h[mb], p.arg(1).slice(0, mb * tm + rank * ts, ts))
+        norm_and_gather(mb, layer_args(0)["attention_norm"], False)
+        chain.join(mb)
+    to_bhsd = lambda z: z.permute((0, 2, 1, 3))
+    for li in range(cfg.n_layer):
+        a = layer_args(li)
+        for mb in range(m):
+            p.event_wait(chain.ready[mb])
+            p.gemm(qkv[mb], xn[mb], a["wqkv"].t())
+            q, k, v = bshd(qkv[mb], 0, hq), bshd(qkv[mb], ql, hkv), bshd(qkv[mb], ql + kl, hkv)
+            p.rope(q, cfg.theta, 0)
+            p.rope(k, cfg.theta, 0)
+            p.attention(to_bhsd(bshd(att[mb], 0, hq)), to_bhsd(q), to_bhsd(k), to_bhsd(v), 1.0 / math.sqrt(hd), True)
+            p.gemm(part[mb], att[mb], a["wo"].t())
+            chain.fork()
+            p.reducescatter(rs[mb], part[mb])
+            p.elementwise("add", h[mb], h[mb], rs[mb])
+            norm_and_gather(mb, a["ffn_norm"], False)
+            chain.join(mb)
+        last = li == cfg.n_layer - 1
+        for mb in range(m):
+            p.event_wait(chain.ready[mb])
+            p.gemm(ff[mb], xn[mb], a["w13"].t(), swiglu=True)
+            p.gemm(part[mb], ff[mb], a["w2"].t())
+            chain.fork()
+            p.reducescatter(rs[mb], part[mb])
+            p.elementwise("add", h[mb], h[mb], rs[mb])
+            norm_and_gather(mb, final_norm if last else layer_args(li + 1)["attention_norm"], last)
+            chain.join(mb)
+    for mb in range(m):
+        p.event_wait(chain.ready[mb])
+    p.reserve_sms(0)
+    return p
+
+
 def flatten_nanogpt_args(w: dict) -> list:
     """Sharded weight dict -> argument list after ``logits, ids`` in plan order."""
     out = [w["wte"], w["wpe"]]

@@ -65,6 +65,24 @@ class PlanSession:
         N.check(rc, self.ctx.handle, "lh_b200_module_op_times")
         return ms
 
+    def timeline_ms(self) -> list[tuple[str, int, float, float]]:
+        """(kind, stream, start, end) per operator of the last profiled run, in ms from the
+        run's start; an operator's start is the end of the previous one on its stream (or its
+        own end for the first), so waits show up as gaps inside the following operator."""
+        n = len(self.plan.ops)
+        ms = np.zeros((n,), dtype=np.float32)
+        rc = self.ctx._lib.lh_b200_module_op_end_times(self.handle, ms.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), n)
+        N.check(rc, self.ctx.handle, "lh_b200_module_op_end_times")
+        out, stream, last = [], 0, {0: 0.0}
+        for op, end in zip(self.plan.ops, ms):
+            if op.kind == "stream":
+                stream = op.attrs["index"]
+                continue
+            start = last.get(stream, float(end))
+            out.append((op.kind, stream, float(start), float(end)))
+            last[stream] = float(end)
+        return out
+
     def close(self) -> None:
         if getattr(self, "handle", None):
             self.ctx._lib.lh_b200_module_destroy(self.handle)

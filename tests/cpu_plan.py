@@ -21,9 +21,10 @@ class CpuPlanRunner:
     """Buffers are flat float64/int arrays (one per slot) holding values already rounded to
     the slot's dtype; views are gathered / scattered with explicit strides."""
 
-    def __init__(self, plan, allreduce=None):
+    def __init__(self, plan, allreduce=None, rank=0, world=1):
         self.plan = plan
-        self.allreduce = allreduce  # callable(np.ndarray) -> np.ndarray, for TP tests
+        self.allreduce = allreduce  # callable(np.ndarray) -> np.ndarray (sum over ranks), for TP tests
+        self.rank, self.world = rank, world
         self.bufs: list[np.ndarray] = []
 
     # -- views -------------------------------------------------------------------------------
@@ -58,7 +59,9 @@ class CpuPlanRunner:
             self.bufs.append(flat.astype(np.int64) if spec.dtype in ("i32", "i64") else flat.astype(np.float64))
         for nbytes in plan.temp_bytes:
             self.bufs.append(np.full(nbytes // 2 + 8, np.nan))  # poison: reads of unwritten temporaries show up
+        self._reset_clocks()
         for op in plan.ops:
+            self._check_ordering(op)
             getattr(self, "_" + op.kind)(op)
         return [self.bufs[i].reshape(spec.shape) for i, spec in enumerate(plan.args)]
 
@@ -129,5 +132,70 @@ class CpuPlanRunner:
         if self.allreduce is not None:
             self.write(v, self.allreduce(self.read(v)))
 
+    def _reducescatter(self, op):
+        out, inp = op.operands[:2]
+        total = self.read(inp) if self.allreduce is None else self.allreduce(self.read(inp))
+        flat = np.asarray(total).reshape(self.world, -1)
+        self.write(out, flat[self.rank].reshape(out.shape))
+
     def _allgather(self, op):
-        raise NotImplementedError
+        out, inp = op.operands[:2]
+        mine = self.read(inp)
+        if self.world == 1:
+            self.write(out, mine.reshape(out.shape))
+            return
+        full = np.zeros((self.world,) + mine.shape)
+        full[self.rank] = mine
+        self.write(out, self.allreduce(full).reshape(out.shape))  # a gather as a sum of disjoint blocks
+
+    # -- two streams -------------------------------------------------------------------------
+    # The interpreter runs both streams in program order, which every correctly synchronised
+    # plan allows, and checks the synchronisation itself with vector clocks: two accesses to
+    # one slot from different streams, at least one of them a write, must be ordered by events.
+    _WRITES = {"gemm": 1, "attention": 1, "layernorm": 1, "rmsnorm": 1, "softmax": 1, "rope": 1, "elementwise": 1,
+               "embedding": 1, "allreduce": 1, "allgather": 1, "reducescatter": 1}
+
+    def _reset_clocks(self):
+        self.cur = 0
+        self.clock = [[0, 0], [0, 0]]  # clock[s][t]: how many operators of stream t stream s has seen
+        self.event_clock: dict[int, list[int]] = {}
+        self.last_write: dict[int, tuple[int, int, str]] = {}
+        self.reads: dict[int, list[tuple[int, int, str]]] = {}
+
+    def _ordered(self, access) -> bool:
+        stream, count, _ = access
+        return self.clock[self.cur][stream] >= count
+
+    def _check_ordering(self, op):
+        if op.kind not in self._WRITES:
+            return
+        self.clock[self.cur][self.cur] += 1
+        me = (self.cur, self.clock[self.cur][self.cur], op.kind)
+        views = [v for v in op.operands if v is not None]
+        out_slot = views[0].slot
+        for v in views[1:] + ([views[0]] if op.kind in ("rope", "allreduce") else []):
+            w = self.last_write.get(v.slot)
+            assert w is None or self._ordered(w), f"{op.kind} on stream {self.cur} reads slot {v.slot} without waiting for {w[2]} on stream {w[0]}"
+        w = self.last_write.get(out_slot)
+        assert w is None or self._ordered(w), f"{op.kind} on stream {self.cur} overwrites slot {out_slot} without waiting for {w[2]} on stream {w[0]}"
+        for r in self.reads.get(out_slot, []):
+            assert self._ordered(r), f"{op.kind} on stream {self.cur} overwrites slot {out_slot} still read by {r[2]} on stream {r[0]}"
+        for v in views[1:]:
+            if v.slot != out_slot:
+                self.reads.setdefault(v.slot, []).append(me)
+        self.last_write[out_slot] = me
+        self.reads[out_slot] = []
+
+    def _stream(self, op):
+        self.cur = op.attrs["index"]
+
+    def _event_record(self, op):
+        self.event_clock[op.attrs["index"]] = list(self.clock[self.cur])
+
+    def _event_wait(self, op):
+        assert op.attrs["index"] in self.event_clock, f"event {op.attrs['index']} waited for before its record"
+        seen = self.event_clock[op.attrs["index"]]
+        self.clock[self.cur] = [max(a, b) for a, b in zip(self.clock[self.cur], seen)]
+
+    def _reserve_sms(self, op):
+        pass

@@ -42,11 +42,11 @@ def run_gpt_rank(cfg, w, ids, rank, tp, allreduce=None):
     return CpuPlanRunner(plan, allreduce).run(args)[0]
 
 
-def run_llama_rank(cfg, w, x, rank, tp, allreduce=None):
-    plan = D.build_llama_plan(cfg, rank, tp)
+def run_llama_rank(cfg, w, x, rank, tp, allreduce=None, overlapped=False):
+    plan = D.build_llama_plan_overlapped(cfg, rank, tp, microbatches=2) if overlapped else D.build_llama_plan(cfg, rank, tp)
     sw = D.shard_llama_weights(w, cfg, rank, tp)
     args = [np.zeros((cfg.tokens, cfg.dim), np.float32), I.to_np(x)] + [I.to_np(t) for t in D.flatten_llama_args(sw)]
-    return CpuPlanRunner(plan, allreduce).run(args)[0]
+    return CpuPlanRunner(plan, allreduce, rank, tp).run(args)[0]
 
 
 def gpt_inputs(cfg):
@@ -119,7 +119,8 @@ def _tp_worker(rank, world, port, q):
         logits = run_gpt_rank(GPT, w, ids, rank, world, allreduce)
         lw, x = llama_inputs(LLAMA)
         hidden = run_llama_rank(LLAMA, lw, x, rank, world, allreduce)
-        q.put((rank, logits, hidden))
+        hidden_overlapped = run_llama_rank(LLAMA, lw, x, rank, world, allreduce, overlapped=True)
+        q.put((rank, logits, hidden, hidden_overlapped))
     finally:
         dist.destroy_process_group()
 
@@ -142,6 +143,31 @@ def test_two_rank_tensor_parallel_matches_single_rank():
     assert max_rel_err(logits, full) < 2e-2
     lw, x = llama_inputs(LLAMA)
     want = llama_reference(LLAMA, lw, x)
-    for _, _, hidden in results:  # the residual stream is replicated after each all-reduce
+    for _, _, hidden, hidden_overlapped in results:  # the residual stream is replicated after each all-reduce
         assert max_rel_err(hidden, want) < 2e-2
+        assert max_rel_err(hidden_overlapped, want) < 2e-2  # reduce-scatter / all-gather schedule
     assert np.array_equal(results[0][2], results[1][2])
+    assert np.array_equal(results[0][3], results[1][3])
+
+
+def test_overlapped_schedule_is_the_same_computation_and_is_fully_ordered():
+    """Micro-batched reduce-scatter / all-gather schedule on one rank: same result as the plain
+    plan up to the extra bf16 roundings of the sharded residual add; the interpreter's
+    vector clocks accept its event ordering, and reject it once a wait is taken out."""
+    w, x = llama_inputs(LLAMA)
+    plain = run_llama_rank(LLAMA, w, x, 0, 1)
+    assert max_rel_err(run_llama_rank(LLAMA, w, x, 0, 1, overlapped=True), plain) < 2e-2
+    plan = D.build_llama_plan_overlapped(LLAMA, 0, 1, microbatches=2)
+    kinds = plan.kinds()
+    n_sub = 2 * LLAMA.n_layer * 2
+    assert kinds.count("reducescatter") == n_sub and kinds.count("allgather") == n_sub + 2
+    assert kinds[0] == "reserve_sms" and kinds[-1] == "reserve_sms"
+    # drop the main stream's wait for the first gathered activations: a read-before-write race
+    waits = [i for i, op in enumerate(plan.ops) if op.kind == "event_wait" and plan.ops[i + 1].kind == "gemm"]
+    del plan.ops[waits[0]]
+    sw = D.shard_llama_weights(w, LLAMA, 0, 1)
+    args = [np.zeros((LLAMA.tokens, LLAMA.dim), np.float32), I.to_np(x)] + [I.to_np(t) for t in D.flatten_llama_args(sw)]
+    with pytest.raises(AssertionError, match="without waiting"):
+        CpuPlanRunner(plan).run(args)
+    with pytest.raises(ValueError):
+        D.build_llama_plan_overlapped(LLAMA, 0, 1, microbatches=3)

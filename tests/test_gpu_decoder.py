@@ -98,6 +98,25 @@ def test_tensor_parallel_shards_sum_to_the_full_model_on_one_gpu(ctx):
     assert bool(torch.isfinite(full).all())
 
 
+def test_overlapped_schedule_on_one_gpu_matches_the_plain_plan(ctx):
+    """The micro-batched two-stream schedule with tp=1 (collectives of a single rank are
+    copies): side stream, numbered events and SM reservation on the real kernels."""
+    cfg = D.LlamaConfig(n_layer=2, dim=256, n_heads=4, n_kv_heads=2, ffn=512, batch=2, seq=256)
+    w = I.llama_weights(cfg.n_layer, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.ffn, seed=7, std=0.05)
+    x = torch.randn(cfg.tokens, cfg.dim, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    plain = run_llama(ctx, cfg, w, x).float()
+    plan = D.build_llama_plan_overlapped(cfg, 0, 1, microbatches=2, reserve_sms=16)
+    outs = []
+    for _ in range(2):
+        out = torch.zeros(cfg.tokens, cfg.dim, device="cuda", dtype=torch.bfloat16)
+        s = PlanSession(plan, ctx=ctx)
+        s.run([out, x.cuda()] + cuda_args(D.flatten_llama_args(D.shard_llama_weights(w, cfg))), sync=True)
+        s.close()
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    assert max_rel_err(outs[0].float().cpu().numpy(), plain.cpu().numpy()) <= TOL_BF16
+
+
 def test_full_size_configs_run_and_are_deterministic(ctx):
     """Config 5 layer shapes (dim 4096, 32/8 heads, FFN 14336, seq 4096) with 1 layer and
     batch 1, and config 4 with 1 layer: finite outputs, bitwise-repeatable."""
