@@ -232,14 +232,31 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
         w = I.llama_weights(cfg.n_layer, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.ffn, seed=5)
         weights = [t.cuda() for t in D.flatten_llama_args(D.shard_llama_weights(w, cfg, tp_rank, tp))]
         overlapped = tp > 1 and args.microbatches > 0
-        plan = D.build_llama_plan_overlapped(cfg, tp_rank, tp, args.microbatches, args.reserve_sms) if overlapped else D.build_llama_plan(cfg, tp_rank, tp)
+        fused = overlapped and args.collectives == "fused"
+        if fused:
+            # symmetric (multicast) buffers for the fused kernel; every rank must get them, or
+            # all ranks take the NCCL schedule together
+            from lighthouse_b200.workloads.symmetric import SymmetricBuffers
+
+            try:
+                symm = SymmetricBuffers(ctx)
+                symm_args = [symm.empty(shape, torch.bfloat16) for shape in D.llama_symmetric_args(cfg, args.microbatches)]
+                failed = 0.0
+            except Exception as e:  # noqa: BLE001 - reported below, never silent
+                print(f"[bench] rank {dist.rank}: symmetric memory unavailable ({e}); NCCL schedule instead", file=sys.stderr)
+                failed = 1.0
+            if dist.sum_over_ranks(failed) > 0:
+                fused = False
+            else:
+                weights += symm_args
+        plan = D.build_llama_plan_overlapped(cfg, tp_rank, tp, args.microbatches, args.reserve_sms, fused=fused) if overlapped else D.build_llama_plan(cfg, tp_rank, tp)
         host_in = torch.randn(cfg.tokens, cfg.dim, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).pin_memory()
         dev_in = host_in.cuda()
         dev_out = torch.empty(cfg.tokens, cfg.dim, device="cuda", dtype=torch.bfloat16)
     else:
         w = I.nanogpt_weights(cfg.n_layer, cfg.n_embd, cfg.hidden, cfg.vocab, cfg.block_size, seed=4)
         weights = [t.cuda() for t in D.flatten_nanogpt_args(D.shard_nanogpt_weights(w, cfg, tp_rank, tp))]
-        overlapped = False
+        overlapped = fused = False
         plan = D.build_nanogpt_plan(cfg, tp_rank, tp)
         ids = torch.randint(0, cfg.vocab, (cfg.tokens * dp,), generator=torch.Generator().manual_seed(1)).to(torch.int32)
         host_in = ids[group * cfg.tokens : (group + 1) * cfg.tokens].contiguous().pin_memory()
@@ -287,7 +304,7 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
         "config": {
             "workload": ("Llama-style decoder stack forward: %d layers, d_model %d, %d q / %d kv heads, head_dim %d, SwiGLU FFN %d, RMSNorm, RoPE, seq %d, batch %d" % (cfg.n_layer, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.seq, cfg.batch))
             if which == "llama" else ("nanoGPT forward: %d layers, d_model %d, %d heads, GELU MLP x4, pre-LayerNorm, causal, seq %d, batch %d, vocab %d" % (cfg.n_layer, cfg.n_embd, cfg.n_head, cfg.seq, cfg.batch * dp, cfg.vocab)),
-            "parallelism": f"tp{tp}" + (f"xdp{dp}" if dp > 1 else "") + (f", reduce-scatter/all-gather of {args.microbatches} micro-batches overlapped with compute" if overlapped else ""), "tokens_per_step": total_tokens, "l2": "inputs_exceed_l2 (weights + activations >> 126 MB)",
+            "parallelism": f"tp{tp}" + (f"xdp{dp}" if dp > 1 else "") + (f", {'fused multimem reduce+norm+gather kernel' if fused else 'NCCL reduce-scatter/all-gather'} of {args.microbatches} micro-batches overlapped with compute" if overlapped else ""), "tokens_per_step": total_tokens, "l2": "inputs_exceed_l2 (weights + activations >> 126 MB)",
             "algorithmic_tflop_per_step": round(flops / 1e12, 3),
         },
         "model_tflops": round(flops / step_s / 1e12, 1), "model_frac_of_peak": round(flops / step_s / 1e12 / (n * peaks["bf16_tflops_sustained"]), 4),
@@ -296,6 +313,8 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
         "gpu_launches": int(launches), "clocks": clocks,
     }
     sess.close()
+    if fused:
+        symm.close()
     ctx.close()
     return res
 
@@ -518,6 +537,7 @@ def main() -> int:
     ap.add_argument("--causal", action="store_true", help="causal mask for the attention workload")
     ap.add_argument("--layers", type=int, default=0, help="override the decoder depth (0 = the configuration's)")
     ap.add_argument("--microbatches", type=int, default=2, help="tensor parallel only: micro-batches whose collectives overlap each other's compute (0: one synchronous all-reduce per contraction)")
+    ap.add_argument("--collectives", choices=["fused", "nccl"], default="fused", help="tensor parallel with micro-batches: one multimem kernel per reduce+norm+gather, or NCCL reduce-scatter / all-gather around row kernels")
     ap.add_argument("--timeline", default="", help="decoder workloads: write rank 0's per-operator timeline of the last timed step to this file")
     ap.add_argument("--reserve-sms", type=int, default=16, help="SMs the persistent GEMMs leave to the collectives in the overlapped schedule")
     ap.add_argument("--no-kernels", action="store_true", help="skip the GEMM / attention kernel lines of the decoder workloads")

@@ -233,6 +233,34 @@ int lh_b200_reducescatter(lh_ctx_t* ctx, const lh_memref_t* out, const lh_memref
 /* out (world * n) = concatenation over ranks of in (n), contiguous. */
 int lh_b200_allgather(lh_ctx_t* ctx, const lh_memref_t* out, const lh_memref_t* in);
 
+/* ------------------------------------------------ fused collective kernels */
+/*
+ * Symmetric memory: buffers that every rank allocates with the same size and role, mapped
+ * into every process (peer pointers) and bound to an NVSwitch multicast object (one address
+ * whose loads can return the sum over all ranks' copies and whose stores reach all of them).
+ * The host allocates and exchanges them (torch.distributed._symmetric_memory in this
+ * repository's workloads) and registers the raw addresses here; the library never maps peer
+ * memory itself. `pads` are the ranks' flag pads (>= 2 * LH_MAX_RANKS * 4 bytes each, zeroed
+ * before the first use) through which the kernels order themselves across ranks; every wait
+ * on them is bounded and ends in LH_ERR_DEVICE at the next lh_b200_sync.
+ */
+#define LH_MAX_RANKS 8
+int lh_b200_symm_register(lh_ctx_t* ctx, void* local, size_t bytes, void* multicast, void* const* peers, int world);
+int lh_b200_symm_set_flags(lh_ctx_t* ctx, int rank, int world, void* const* pads);
+int lh_b200_symm_clear(lh_ctx_t* ctx);
+/*
+ * What follows a tensor-parallel contraction, as one kernel on world ranks (rows = h's rows;
+ * this rank owns rows [rank * rows, (rank + 1) * rows) of xn and part):
+ *   h   <- h + sum over ranks of part[my rows]        (part == NULL: h unchanged)
+ *   xn[my rows] on EVERY rank <- rmsnorm(h) * weight
+ * i.e. reduce-scatter, residual add, RMSNorm (ref_model.py:24-47) and all-gather. xn and part
+ * must lie in registered regions with a multicast mapping; with one rank and no
+ * registration the same arithmetic runs on local memory. bf16 activations, row length a
+ * multiple of 8 and at most 4096. Every rank must make the same sequence of these calls.
+ */
+int lh_b200_reduce_norm_gather(lh_ctx_t* ctx, const lh_memref_t* xn, const lh_memref_t* part, const lh_memref_t* h,
+                               const lh_memref_t* weight, float eps);
+
 /* ----------------------------------------------------- side stream / events */
 /*
  * A context owns a second, high-priority stream for work that should overlap the main
@@ -274,7 +302,8 @@ typedef enum {
   LH_OP_STREAM = 12,
   LH_OP_EVENT_RECORD = 13,
   LH_OP_EVENT_WAIT = 14,
-  LH_OP_RESERVE_SMS = 15
+  LH_OP_RESERVE_SMS = 15,
+  LH_OP_REDUCE_NORM_GATHER = 16
 } lh_op_kind_t;
 
 /* An operand: a view into a slot. slot < 0 means "absent". */
@@ -304,6 +333,7 @@ typedef struct {
  *   STREAM      (none)                          i0 = 0 main / 1 side
  *   EVENT_RECORD, EVENT_WAIT (none)             i0 = event number
  *   RESERVE_SMS (none)                          i0 = SMs left free by persistent kernels
+ *   REDUCE_NORM_GATHER xn, part, h, weight      f0 = eps
  */
 typedef struct {
   int32_t kind;

@@ -192,6 +192,44 @@ class CudaContext:
         N.check(self._lib.lh_b200_allgather(self.handle, _ref(mo), _ref(mi)), self.handle, "lh_b200_allgather")
 
 
+    def reducescatter(self, out, inp) -> None:
+        mo, mi = as_memref(out), as_memref(inp)
+        N.check(self._lib.lh_b200_reducescatter(self.handle, _ref(mo), _ref(mi)), self.handle, "lh_b200_reducescatter")
+
+    # -- side stream ------------------------------------------------------------------
+    def stream_select(self, side: int) -> None:
+        N.check(self._lib.lh_b200_stream_select(self.handle, int(side)), self.handle, "lh_b200_stream_select")
+
+    def event_record(self, number: int) -> None:
+        N.check(self._lib.lh_b200_event_record(self.handle, int(number)), self.handle, "lh_b200_event_record")
+
+    def event_wait(self, number: int) -> None:
+        N.check(self._lib.lh_b200_event_wait(self.handle, int(number)), self.handle, "lh_b200_event_wait")
+
+    def reserve_sms(self, n: int) -> None:
+        N.check(self._lib.lh_b200_reserve_sms(self.handle, int(n)), self.handle, "lh_b200_reserve_sms")
+
+    # -- symmetric memory and the fused collective ------------------------------------------
+    def symm_register(self, local_ptr: int, nbytes: int, multicast_ptr: int, peer_ptrs: list[int]) -> None:
+        """Registers one symmetric buffer: this rank's address, its multicast mapping (0: none)
+        and every rank's copy as mapped into this process."""
+        peers = (ctypes.c_void_p * len(peer_ptrs))(*peer_ptrs)
+        rc = self._lib.lh_b200_symm_register(self.handle, ctypes.c_void_p(local_ptr), int(nbytes), ctypes.c_void_p(multicast_ptr or None), peers, len(peer_ptrs))
+        N.check(rc, self.handle, "lh_b200_symm_register")
+
+    def symm_set_flags(self, rank: int, world: int, pad_ptrs: list[int]) -> None:
+        pads = (ctypes.c_void_p * len(pad_ptrs))(*pad_ptrs)
+        N.check(self._lib.lh_b200_symm_set_flags(self.handle, int(rank), int(world), pads), self.handle, "lh_b200_symm_set_flags")
+
+    def symm_clear(self) -> None:
+        N.check(self._lib.lh_b200_symm_clear(self.handle), self.handle, "lh_b200_symm_clear")
+
+    def reduce_norm_gather(self, xn, part, h, weight, eps: float = 1e-5) -> None:
+        mx, mp, mh, mw = (as_memref(t) for t in (xn, part, h, weight))
+        rc = self._lib.lh_b200_reduce_norm_gather(self.handle, _ref(mx), _ref(mp), _ref(mh), _ref(mw), float(eps))
+        N.check(rc, self.handle, "lh_b200_reduce_norm_gather")
+
+
 def nccl_unique_id(nccl_path: str | None = None) -> bytes:
     """128-byte NCCL unique id for ``CudaContext.comm_init`` (rank 0 creates, everyone receives)."""
     buf = ctypes.create_string_buffer(128)

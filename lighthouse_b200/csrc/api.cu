@@ -200,6 +200,7 @@ extern "C" int lh_b200_ctx_destroy(lh_ctx_t* ctx) {
   for (cudaEvent_t e : ctx->events)
     if (e) cudaEventDestroy(e);
   if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->symm_counter) cudaFree(ctx->symm_counter);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
   if (ctx->host_status) cudaFreeHost(ctx->host_status);
   delete ctx;
@@ -627,7 +628,7 @@ extern "C" int lh_b200_module_create(lh_ctx_t* ctx, const char* entry_name, cons
   *out = nullptr;
   const int nslots = nargs + ntemps;
   for (int i = 0; i < nops; ++i) {
-    if (ops[i].kind < LH_OP_GEMM || ops[i].kind > LH_OP_RESERVE_SMS) return set_error(ctx, LH_ERR_INVALID, "module_create: op %d has unknown kind %d", i, ops[i].kind);
+    if (ops[i].kind < LH_OP_GEMM || ops[i].kind > LH_OP_REDUCE_NORM_GATHER) return set_error(ctx, LH_ERR_INVALID, "module_create: op %d has unknown kind %d", i, ops[i].kind);
     for (int j = 0; j < LH_MAX_OPERANDS; ++j) {
       const lh_view_t& v = ops[i].operands[j];
       if (v.slot >= nslots) return set_error(ctx, LH_ERR_INVALID, "module_create: op %d operand %d names slot %d of %d", i, j, v.slot, nslots);
@@ -703,6 +704,7 @@ static int run_ops(lh_module* m, void* const* arg_ptrs) {
       case LH_OP_EVENT_RECORD: rc = lh_b200_event_record(ctx, op.i0); break;
       case LH_OP_EVENT_WAIT: rc = lh_b200_event_wait(ctx, op.i0); break;
       case LH_OP_RESERVE_SMS: rc = lh_b200_reserve_sms(ctx, op.i0); break;
+      case LH_OP_REDUCE_NORM_GATHER: rc = lh_b200_reduce_norm_gather(ctx, o[0], o[1], o[2], o[3], op.f0); break;
       case LH_OP_ALLGATHER: rc = lh_b200_allgather(ctx, o[0], o[1]); break;
       default: rc = set_error(ctx, LH_ERR_INVALID, "unknown op kind %d", op.kind);
     }

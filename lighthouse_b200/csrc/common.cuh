@@ -15,6 +15,16 @@
 
 #include "../../include/lh_b200.h"
 
+// A buffer allocated symmetrically on every rank (same size, same role): its address here,
+// its NVSwitch multicast mapping (one address that reaches all ranks' copies) and the ranks'
+// copies as mapped into this process.
+struct SymmRegion {
+  char* local;
+  size_t bytes;
+  char* multicast;
+  char* peers[LH_MAX_RANKS];
+};
+
 struct lh_ctx {
   int device = 0;
   int sm_count = 0;
@@ -40,6 +50,12 @@ struct lh_ctx {
   bool side_selected = false;
   std::vector<cudaEvent_t> events;    // indexed by event number, created on first use
   int reserved_sms = 0;               // SMs persistent kernels leave free
+  // symmetric memory for the fused collectives
+  std::vector<SymmRegion> symm;
+  uint32_t* symm_pads[LH_MAX_RANKS] = {nullptr};  // every rank's flag pad as mapped here
+  int symm_rank = 0, symm_world = 0;
+  uint32_t symm_epoch = 0;            // launches of flag-synchronised kernels so far (same on every rank)
+  uint32_t* symm_counter = nullptr;   // device word: blocks finished in the running launch
 };
 
 namespace lh {

@@ -180,6 +180,7 @@ _KIND_CODES = {
     "event_record": N.OP_EVENT_RECORD,
     "event_wait": N.OP_EVENT_WAIT,
     "reserve_sms": N.OP_RESERVE_SMS,
+    "reduce_norm_gather": N.OP_REDUCE_NORM_GATHER,
 }
 
 
@@ -254,6 +255,13 @@ class Plan:
         self.ops.append(PlanOp("reducescatter", [out, inp]))
         return out
 
+    def reduce_norm_gather(self, xn, part, h, weight, eps: float):
+        """Fused reduce-scatter + residual add + RMSNorm + all-gather over symmetric memory:
+        ``h += sum over ranks of part[my rows]`` (skipped when ``part`` is None), then
+        ``xn[my rows]`` on every rank ``= rmsnorm(h) * weight``."""
+        self.ops.append(PlanOp("reduce_norm_gather", [xn, part, h, weight], {"eps": float(eps)}))
+        return xn
+
     # -- side stream: operators after ``stream(1)`` go to the context's second stream until
     # ``stream(0)``; numbered events order the two streams.
     def stream(self, side: int):
@@ -304,7 +312,7 @@ class Plan:
                 o.i0, o.i1 = ACT_CODES[at.get("act", "none")], int(at.get("flags", 0))
             elif op.kind == "attention":
                 o.f0, o.i0 = at["scale"], int(at.get("causal", False))
-            elif op.kind in ("layernorm", "rmsnorm"):
+            elif op.kind in ("layernorm", "rmsnorm", "reduce_norm_gather"):
                 o.f0 = at.get("eps", 1e-5)
             elif op.kind == "rope":
                 o.f0, o.i0 = at.get("theta", 10000.0), at.get("pos0", 0)

@@ -307,14 +307,20 @@ def check_overlap(tokens: int, batch: int, tp: int, microbatches: int) -> None:
 
 
 def build_llama_plan_overlapped(cfg: LlamaConfig, rank: int, tp: int, microbatches: int = 2, reserve_sms: int = 16,
-                                name: str = "llama_forward") -> Plan:
+                                name: str = "llama_forward", fused: bool = False) -> Plan:
     """Same arguments and result as ``build_llama_plan``; different schedule for ``tp`` > 1.
 
     The all-reduce after each contraction is split into reduce-scatter + all-gather with the
     residual stream sharded by rows between them (each rank adds the residual and normalises
     1/tp of the tokens instead of all of them), and the batch is cut into micro-batches of
     whole sequences so that one micro-batch's collectives run on the side stream under the
-    other's GEMMs and attention. Only the last collective of the step is exposed."""
+    other's GEMMs and attention. Only the last collective of the step is exposed.
+
+    ``fused``: reduce-scatter, residual add, RMSNorm and all-gather are ONE kernel over NVSwitch
+    multicast memory (``lh_b200_reduce_norm_gather``) instead of two NCCL calls around two
+    row kernels. The partial-sum and gathered-activation buffers are then symmetric memory
+    the caller allocates: ``2 * microbatches`` extra arguments after ``norm``, per micro-batch
+    ``part (tokens/microbatches, dim)`` then ``xn`` (same shape), see ``llama_symmetric_args``."""
     check_tp(cfg, tp)
     check_overlap(cfg.tokens, cfg.batch, tp, microbatches)
     d, t, hd = cfg.dim, cfg.tokens, cfg.head_dim
@@ -326,28 +332,42 @@ def build_llama_plan_overlapped(cfg: LlamaConfig, rank: int, tp: int, microbatch
     for li in range(cfg.n_layer):
         args += [ArgSpec(s, dt, f"l{li}.{k}") for (s, dt), k in zip(per_layer, LLAMA_LAYER_KEYS)]
     args.append(ArgSpec((d,), "bf16", "norm"))
-    p = Plan(name, args)
+    norm_index = len(args) - 1
     m = microbatches
     bm, tm = cfg.batch // m, t // m
     ts = tm // tp
+    if fused:
+        for mb in range(m):
+            args += [ArgSpec((tm, d), "bf16", f"part{mb}"), ArgSpec((tm, d), "bf16", f"xn{mb}")]
+    p = Plan(name, args)
     h = [p.temp((ts, d), "bf16") for _ in range(m)]       # this rank's rows of the residual stream
-    xn = [p.temp((tm, d), "bf16") for _ in range(m)]      # gathered normalised activations
+    # gathered normalised activations and this rank's partial sums of a contraction
+    xn = [p.arg(norm_index + 2 + 2 * mb) if fused else p.temp((tm, d), "bf16") for mb in range(m)]
+    part = [p.arg(norm_index + 1 + 2 * mb) if fused else p.temp((tm, d), "bf16") for mb in range(m)]
     qkv = [p.temp((tm, width), "bf16") for _ in range(m)]
     att = [p.temp((tm, ql), "bf16") for _ in range(m)]
     ff = [p.temp((tm, fl), "bf16") for _ in range(m)]
-    part = [p.temp((tm, d), "bf16") for _ in range(m)]    # this rank's partial sums of a contraction
-    rs = [p.temp((ts, d), "bf16") for _ in range(m)]
+    rs = [None if fused else p.temp((ts, d), "bf16") for _ in range(m)]
     chain = _SideChain(p, m)
     layer_args = lambda li: {k: p.arg(2 + li * len(LLAMA_LAYER_KEYS) + i) for i, k in enumerate(LLAMA_LAYER_KEYS)}
-    final_norm = p.arg(len(args) - 1)
+    final_norm = p.arg(norm_index)
 
     def bshd(view2d: PView, col0: int, nheads: int) -> PView:
         v = view2d.slice(1, col0, nheads * hd)
         return PView(v.slot, (bm, cfg.seq, nheads, hd), (cfg.seq * v.strides[0], v.strides[0], hd, 1), v.dtype, v.offset)
 
-    def norm_and_gather(mb: int, weight: PView, last: bool) -> None:
-        """On the side stream: normalise this rank's rows into their place in the gathered
-        buffer (the result argument itself after the last layer) and all-gather in place."""
+    def norm_and_gather(mb: int, weight: PView, last: bool, reduce: bool = True) -> None:
+        """On the side stream: (sum the partial sums of this rank's rows into the residual
+        stream,) normalise those rows into their place in the gathered buffer (the result
+        argument itself after the last layer) and gather."""
+        if fused:
+            p.reduce_norm_gather(xn[mb], part[mb] if reduce else None, h[mb], weight, cfg.eps)
+            if last:
+                p.elementwise("copy", p.arg(0).slice(0, mb * tm, tm), xn[mb])
+            return
+        if reduce:
+            p.reducescatter(rs[mb], part[mb])
+            p.elementwise("add", h[mb], h[mb], rs[mb])
         full = p.arg(0).slice(0, mb * tm, tm) if last else xn[mb]
         mine = full.slice(0, rank * ts, ts)
         p.rmsnorm(mine, h[mb], weight, cfg.eps)
@@ -357,7 +377,7 @@ def build_llama_plan_overlapped(cfg: LlamaConfig, rank: int, tp: int, microbatch
     for mb in range(m):
         chain.fork()
         p.elementwise("copy", h[mb], p.arg(1).slice(0, mb * tm + rank * ts, ts))
-        norm_and_gather(mb, layer_args(0)["attention_norm"], False)
+        norm_and_gather(mb, layer_args(0)["attention_norm"], False, reduce=False)
         chain.join(mb)
     to_bhsd = lambda z: z.permute((0, 2, 1, 3))
     for li in range(cfg.n_layer):
@@ -371,8 +391,6 @@ def build_llama_plan_overlapped(cfg: LlamaConfig, rank: int, tp: int, microbatch
             p.attention(to_bhsd(bshd(att[mb], 0, hq)), to_bhsd(q), to_bhsd(k), to_bhsd(v), 1.0 / math.sqrt(hd), True)
             p.gemm(part[mb], att[mb], a["wo"].t())
             chain.fork()
-            p.reducescatter(rs[mb], part[mb])
-            p.elementwise("add", h[mb], h[mb], rs[mb])
             norm_and_gather(mb, a["ffn_norm"], False)
             chain.join(mb)
         last = li == cfg.n_layer - 1
@@ -381,14 +399,18 @@ def build_llama_plan_overlapped(cfg: LlamaConfig, rank: int, tp: int, microbatch
             p.gemm(ff[mb], xn[mb], a["w13"].t(), swiglu=True)
             p.gemm(part[mb], ff[mb], a["w2"].t())
             chain.fork()
-            p.reducescatter(rs[mb], part[mb])
-            p.elementwise("add", h[mb], h[mb], rs[mb])
             norm_and_gather(mb, final_norm if last else layer_args(li + 1)["attention_norm"], last)
             chain.join(mb)
     for mb in range(m):
         p.event_wait(chain.ready[mb])
     p.reserve_sms(0)
     return p
+
+
+def llama_symmetric_args(cfg: LlamaConfig, microbatches: int) -> list[tuple[int, int]]:
+    """Shapes (bf16) of the symmetric buffers the fused schedule takes after ``norm``."""
+    tm = cfg.tokens // microbatches
+    return [(tm, cfg.dim)] * (2 * microbatches)
 
 
 def flatten_nanogpt_args(w: dict) -> list:

@@ -148,12 +148,29 @@ class CpuPlanRunner:
         full[self.rank] = mine
         self.write(out, self.allreduce(full).reshape(out.shape))  # a gather as a sum of disjoint blocks
 
+    def _reduce_norm_gather(self, op):
+        xn, part, h, w = op.operands[:4]
+        rows = h.shape[0]
+        mine = slice(self.rank * rows, (self.rank + 1) * rows)
+        hv = self.read(h)
+        if part is not None:
+            parts = R.round_to(self.read(part).astype(np.float32), "bf16").astype(np.float64)
+            total = parts if self.allreduce is None else self.allreduce(parts)
+            total = R.round_to(np.asarray(total, dtype=np.float32), "bf16")  # the switch returns the activation type
+            hv = hv.astype(np.float32) + total[mine]
+            self.write(h, hv)
+            hv = self.read(h)
+        normed = R.round_to(R.rmsnorm(hv, self.read(w), op.attrs["eps"], xn.dtype).astype(np.float32), xn.dtype)
+        full = np.zeros(xn.shape)
+        full[mine] = normed
+        self.write(xn, full if self.world == 1 else self.allreduce(full))
+
     # -- two streams -------------------------------------------------------------------------
     # The interpreter runs both streams in program order, which every correctly synchronised
     # plan allows, and checks the synchronisation itself with vector clocks: two accesses to
     # one slot from different streams, at least one of them a write, must be ordered by events.
     _WRITES = {"gemm": 1, "attention": 1, "layernorm": 1, "rmsnorm": 1, "softmax": 1, "rope": 1, "elementwise": 1,
-               "embedding": 1, "allreduce": 1, "allgather": 1, "reducescatter": 1}
+               "embedding": 1, "allreduce": 1, "allgather": 1, "reducescatter": 1, "reduce_norm_gather": 1}
 
     def _reset_clocks(self):
         self.cur = 0
@@ -185,6 +202,9 @@ class CpuPlanRunner:
                 self.reads.setdefault(v.slot, []).append(me)
         self.last_write[out_slot] = me
         self.reads[out_slot] = []
+        if op.kind == "reduce_norm_gather":  # also updates the residual rows (operand 2)
+            self.last_write[op.operands[2].slot] = me
+            self.reads[op.operands[2].slot] = []
 
     def _stream(self, op):
         self.cur = op.attrs["index"]

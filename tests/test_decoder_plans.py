@@ -42,10 +42,12 @@ def run_gpt_rank(cfg, w, ids, rank, tp, allreduce=None):
     return CpuPlanRunner(plan, allreduce).run(args)[0]
 
 
-def run_llama_rank(cfg, w, x, rank, tp, allreduce=None, overlapped=False):
-    plan = D.build_llama_plan_overlapped(cfg, rank, tp, microbatches=2) if overlapped else D.build_llama_plan(cfg, rank, tp)
+def run_llama_rank(cfg, w, x, rank, tp, allreduce=None, overlapped=False, fused=False):
+    plan = D.build_llama_plan_overlapped(cfg, rank, tp, microbatches=2, fused=fused) if overlapped else D.build_llama_plan(cfg, rank, tp)
     sw = D.shard_llama_weights(w, cfg, rank, tp)
     args = [np.zeros((cfg.tokens, cfg.dim), np.float32), I.to_np(x)] + [I.to_np(t) for t in D.flatten_llama_args(sw)]
+    if fused:
+        args += [np.zeros(shape, np.float32) for shape in D.llama_symmetric_args(cfg, 2)]
     return CpuPlanRunner(plan, allreduce, rank, tp).run(args)[0]
 
 
@@ -120,7 +122,8 @@ def _tp_worker(rank, world, port, q):
         lw, x = llama_inputs(LLAMA)
         hidden = run_llama_rank(LLAMA, lw, x, rank, world, allreduce)
         hidden_overlapped = run_llama_rank(LLAMA, lw, x, rank, world, allreduce, overlapped=True)
-        q.put((rank, logits, hidden, hidden_overlapped))
+        hidden_fused = run_llama_rank(LLAMA, lw, x, rank, world, allreduce, overlapped=True, fused=True)
+        q.put((rank, logits, hidden, hidden_overlapped, hidden_fused))
     finally:
         dist.destroy_process_group()
 
@@ -143,11 +146,12 @@ def test_two_rank_tensor_parallel_matches_single_rank():
     assert max_rel_err(logits, full) < 2e-2
     lw, x = llama_inputs(LLAMA)
     want = llama_reference(LLAMA, lw, x)
-    for _, _, hidden, hidden_overlapped in results:  # the residual stream is replicated after each all-reduce
+    for _, _, hidden, hidden_overlapped, hidden_fused in results:  # the residual stream is replicated after each all-reduce
         assert max_rel_err(hidden, want) < 2e-2
         assert max_rel_err(hidden_overlapped, want) < 2e-2  # reduce-scatter / all-gather schedule
-    assert np.array_equal(results[0][2], results[1][2])
-    assert np.array_equal(results[0][3], results[1][3])
+        assert max_rel_err(hidden_fused, want) < 2e-2  # one fused reduce + norm + gather per sub-block
+    for i in (2, 3, 4):
+        assert np.array_equal(results[0][i], results[1][i])
 
 
 def test_overlapped_schedule_is_the_same_computation_and_is_fully_ordered():
@@ -171,3 +175,8 @@ def test_overlapped_schedule_is_the_same_computation_and_is_fully_ordered():
         CpuPlanRunner(plan).run(args)
     with pytest.raises(ValueError):
         D.build_llama_plan_overlapped(LLAMA, 0, 1, microbatches=3)
+    # the fused form: same schedule, one operator per side chain, symmetric buffers as arguments
+    fused = D.build_llama_plan_overlapped(LLAMA, 0, 1, microbatches=2, fused=True)
+    assert fused.kinds().count("reduce_norm_gather") == n_sub + 2 and "reducescatter" not in fused.kinds()
+    assert len(fused.args) == len(plan.args) + 4 and fused.args[-1].name == "xn1"
+    assert max_rel_err(run_llama_rank(LLAMA, w, x, 0, 1, overlapped=True, fused=True), plain) < 2e-2

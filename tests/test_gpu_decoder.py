@@ -117,6 +117,39 @@ def test_overlapped_schedule_on_one_gpu_matches_the_plain_plan(ctx):
     assert max_rel_err(outs[0].float().cpu().numpy(), plain.cpu().numpy()) <= TOL_BF16
 
 
+def test_fused_schedule_on_one_gpu_matches_the_plain_plan(ctx):
+    """The fused reduce + norm + gather operator in its single-rank form (plain loads and
+    stores instead of multimem), inside the micro-batched schedule."""
+    cfg = D.LlamaConfig(n_layer=2, dim=256, n_heads=4, n_kv_heads=2, ffn=512, batch=2, seq=256)
+    w = I.llama_weights(cfg.n_layer, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.ffn, seed=7, std=0.05)
+    x = torch.randn(cfg.tokens, cfg.dim, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    plain = run_llama(ctx, cfg, w, x).float()
+    plan = D.build_llama_plan_overlapped(cfg, 0, 1, microbatches=2, reserve_sms=16, fused=True)
+    out = torch.zeros(cfg.tokens, cfg.dim, device="cuda", dtype=torch.bfloat16)
+    extra = [torch.zeros(shape, device="cuda", dtype=torch.bfloat16) for shape in D.llama_symmetric_args(cfg, 2)]
+    s = PlanSession(plan, ctx=ctx)
+    s.run([out, x.cuda()] + cuda_args(D.flatten_llama_args(D.shard_llama_weights(w, cfg))) + extra, sync=True)
+    s.close()
+    assert max_rel_err(out.float().cpu().numpy(), plain.cpu().numpy()) <= TOL_BF16
+
+
+@pytest.mark.parametrize("rows,n,with_part", [(96, 4096, True), (7, 256, True), (130, 1024, False)])
+def test_reduce_norm_gather_single_rank_matches_oracle(ctx, rows, n, with_part):
+    g = torch.Generator().manual_seed(rows + n)
+    h = torch.randn(rows, n, generator=g).to(torch.bfloat16)
+    part = torch.randn(rows, n, generator=g).to(torch.bfloat16)
+    wgt = (1 + 0.1 * torch.randn(n, generator=g)).to(torch.bfloat16)
+    hd, pd, wd, xn = h.cuda(), part.cuda(), wgt.cuda(), torch.zeros(rows, n, device="cuda", dtype=torch.bfloat16)
+    ctx.reduce_norm_gather(xn, pd if with_part else None, hd, wd, 1e-5)
+    ctx.sync()
+    h_ref = R.round_to(I.to_np(h) + I.to_np(part), "bf16") if with_part else I.to_np(h)
+    assert np.array_equal(hd.float().cpu().numpy(), h_ref)  # the residual update is exact in bf16
+    want = R.rmsnorm(h_ref, I.to_np(wgt), 1e-5, "bf16")
+    assert max_rel_err(xn.float().cpu().numpy(), want) <= TOL_BF16
+    with pytest.raises(ValueError):
+        ctx.reduce_norm_gather(xn, None, hd[:, : n - 4], wd, 1e-5)
+
+
 def test_full_size_configs_run_and_are_deterministic(ctx):
     """Config 5 layer shapes (dim 4096, 32/8 heads, FFN 14336, seq 4096) with 1 layer and
     batch 1, and config 4 with 1 layer: finite outputs, bitwise-repeatable."""
