@@ -35,6 +35,7 @@ struct Attn2Params {
   float scale_log2;
   int causal;
   int num_q_tiles;
+  int pair_slots;  // causal: blocks below this count are placed one per SM first (0: plain order)
   int* dev_status;
 };
 
@@ -89,8 +90,22 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int bh = blockIdx.x / p.num_q_tiles;
-  const int qt = p.num_q_tiles - 1 - (blockIdx.x % p.num_q_tiles);  // longest causal rows first
+  // Work order. A causal query tile qt visits qt + 1 key tiles, so tiles are handed out
+  // heaviest first (every (batch, head) of the last tile, then of the one before, ...): late
+  // blocks are short and the tail of the grid is too. When the whole grid is resident at once
+  // (two blocks per SM), the second block of each SM instead comes from the light end, so
+  // that a long block shares its SM with a short one and has it alone for most of its run.
+  int bh, qt;
+  if (p.causal) {
+    const int total = gridDim.x, nbh = total / p.num_q_tiles;
+    int r = blockIdx.x;
+    if (p.pair_slots > 0 && r >= p.pair_slots) r = total - 1 - (r - p.pair_slots);
+    qt = p.num_q_tiles - 1 - r / nbh;
+    bh = r % nbh;
+  } else {
+    bh = blockIdx.x / p.num_q_tiles;
+    qt = blockIdx.x % p.num_q_tiles;
+  }
   const int b = bh / p.Hq;
   const int hq = bh % p.Hq;
   const int hkv = hq / (p.Hq / p.Hkv);
@@ -361,6 +376,7 @@ int launch2_hd(lh_ctx* ctx, const AttnProblem& a) {
   auto kernel = attn_fwd_tc2_kernel<HD>;
   LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   const int64_t grid = static_cast<int64_t>(a.B) * a.Hq * p.num_q_tiles;
+  p.pair_slots = (grid > ctx->sm_count && grid <= 2 * static_cast<int64_t>(ctx->sm_count)) ? ctx->sm_count : 0;
   kernel<<<static_cast<unsigned>(grid), ATT2_THREADS, L::DYN_BYTES, ctx->stream>>>(tmQ, tmK, tmV, p);
   LH_CHECK_LAUNCH(ctx, "attn_fwd_tc2_kernel");
   return LH_OK;
