@@ -282,17 +282,39 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
                     f.write(f"{kind:14s} stream {strm}  {t0:9.3f} -> {t1:9.3f} ms  ({t1 - t0:7.3f})\n")
         sess.set_profiling(False)
 
+        # End to end: host -> device copy of the step's input, the step, device -> host read of
+        # the result. In the overlapped schedules a rank reads only its own rows of the input
+        # (the residual stream is sharded by rows) and every rank ends up with the whole
+        # result, so each copies its own rows in and reads its own rows back: together the
+        # ranks move the input and the result exactly once.
+        if overlapped:
+            tm = cfg.tokens // args.microbatches
+            ts = tm // tp
+            my_rows = [slice(mb * tm + tp_rank * ts, mb * tm + (tp_rank + 1) * ts) for mb in range(args.microbatches)]
+        else:
+            my_rows = None
+
         def e2e_step():
-            dev_in.copy_(host_in, non_blocking=True)
+            if my_rows:
+                for rows in my_rows:
+                    dev_in[rows].copy_(host_in[rows], non_blocking=True)
+            else:
+                dev_in.copy_(host_in, non_blocking=True)
             sess.run(dev_args)
-            if dist.rank % tp == 0 or which == "nanogpt":
+            if my_rows:
+                for rows in my_rows:
+                    host_out[rows].copy_(dev_out[rows], non_blocking=True)
+            elif dist.rank % tp == 0 or which == "nanogpt":
                 host_out.copy_(dev_out, non_blocking=True)
 
         ms_e2e = timed_loop(dist, stream, e2e_step, args.steps, max(1, args.warmup // 2))
         clocks = sampler.stop()
     ctx.sync()  # raises if any kernel gave up on a bounded wait
-    h2d = host_in.numel() * host_in.element_size()
-    d2h = host_out.numel() * host_out.element_size() if (dist.rank % tp == 0 or which == "nanogpt") else 0
+    if my_rows:
+        h2d = d2h = sum(r.stop - r.start for r in my_rows) * host_in.shape[1] * host_in.element_size()
+    else:
+        h2d = host_in.numel() * host_in.element_size()
+        d2h = host_out.numel() * host_out.element_size() if (dist.rank % tp == 0 or which == "nanogpt") else 0
     h2d_total, d2h_total = dist.sum_over_ranks(h2d), dist.sum_over_ranks(d2h)
     peaks, source = load_peaks()
     flops = cfg.flops_per_token() * total_tokens

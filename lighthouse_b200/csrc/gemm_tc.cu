@@ -469,12 +469,13 @@ int pick_bn(const lh_ctx* ctx, const GemmProblem& p) {
   const int cand[3] = {256, 192, 128};
   const double eff[3] = {1.0, 0.88, 0.72};  // measured on 4096 x 4096 x K problems
   const int num_m = (p.M + BM - 1) / BM;
+  const int sms = ctx->sm_count - ctx->reserved_sms > 0 ? ctx->sm_count - ctx->reserved_sms : 1;  // the grid's size
   int best = 256;
   double best_cost = 1e300;
   for (int i = 0; i < 3; ++i) {
     const int bn = cand[i];
     const int64_t tiles = static_cast<int64_t>(num_m) * ((p.N + bn - 1) / bn);
-    const int64_t waves = (tiles + ctx->sm_count - 1) / ctx->sm_count;
+    const int64_t waves = (tiles + sms - 1) / sms;
     const double cost = static_cast<double>(waves) * bn / eff[i];
     if (cost < best_cost - 1e-9) {
       best_cost = cost;

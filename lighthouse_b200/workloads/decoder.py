@@ -372,12 +372,15 @@ def build_llama_plan_overlapped(cfg: LlamaConfig, rank: int, tp: int, microbatch
         p.rmsnorm(mine, h[mb], weight, cfg.eps)
         p.allgather(full, mine)
 
-    p.reserve_sms(reserve_sms)
+    # Nothing runs beside the first micro-batch's first chain and the last one's last chain:
+    # they get the whole GPU; in between the GEMMs leave ``reserve_sms`` SMs to the side stream.
     for mb in range(m):
         chain.fork()
         p.elementwise("copy", h[mb], p.arg(1).slice(0, mb * tm + rank * ts, ts))
         norm_and_gather(mb, layer_args(0)["attention_norm"], False, reduce=False)
         chain.join(mb)
+        if mb == 0:
+            p.reserve_sms(reserve_sms)
     to_bhsd = lambda z: z.permute((0, 2, 1, 3))
     for li in range(cfg.n_layer):
         a = layer_args(li)
@@ -396,12 +399,13 @@ def build_llama_plan_overlapped(cfg: LlamaConfig, rank: int, tp: int, microbatch
             p.event_wait(chain.ready[mb])
             p.gemm(ff[mb], xn[mb], a["w13"].t(), swiglu=True)
             p.gemm(part[mb], ff[mb], a["w2"].t())
+            if last and mb == m - 1:
+                p.reserve_sms(0)
             chain.fork()
             norm_and_gather(mb, final_norm if last else layer_args(li + 1)["attention_norm"], last)
             chain.join(mb)
     for mb in range(m):
         p.event_wait(chain.ready[mb])
-    p.reserve_sms(0)
     return p
 
 

@@ -165,9 +165,9 @@ def test_overlapped_schedule_is_the_same_computation_and_is_fully_ordered():
     kinds = plan.kinds()
     n_sub = 2 * LLAMA.n_layer * 2
     assert kinds.count("reducescatter") == n_sub and kinds.count("allgather") == n_sub + 2
-    assert kinds[0] == "reserve_sms" and kinds[-1] == "reserve_sms"
+    assert kinds.count("reserve_sms") == 2 and plan.ops[[i for i, k in enumerate(kinds) if k == "reserve_sms"][-1]].attrs["index"] == 0
     # drop the main stream's wait for the first gathered activations: a read-before-write race
-    waits = [i for i, op in enumerate(plan.ops) if op.kind == "event_wait" and plan.ops[i + 1].kind == "gemm"]
+    waits = [i for i, op in enumerate(plan.ops) if op.kind == "event_wait" and i + 1 < len(plan.ops) and plan.ops[i + 1].kind == "gemm"]
     del plan.ops[waits[0]]
     sw = D.shard_llama_weights(w, LLAMA, 0, 1)
     args = [np.zeros((LLAMA.tokens, LLAMA.dim), np.float32), I.to_np(x)] + [I.to_np(t) for t in D.flatten_llama_args(sw)]

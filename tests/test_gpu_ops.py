@@ -294,3 +294,36 @@ def test_launch_counter_and_status_word(ctx):
     ctx.elementwise(N.EW_FILL, t, scalar=1.0)
     ctx.sync()  # also reads the device status word: no bounded wait ran out
     assert ctx.launch_count == before + 1 and float(t.sum()) == 64.0
+
+
+def test_side_stream_events_and_collectives_of_one_rank(ctx):
+    """The two-stream mechanism the overlapped schedules use: work on the side stream starts
+    after the main stream's record and the main stream resumes after the side stream's."""
+    a = torch.ones(1 << 22, device="cuda")
+    b, c = torch.zeros_like(a), torch.zeros_like(a)
+    torch.cuda.synchronize()
+    ctx.reserve_sms(8)
+    ctx.elementwise(N.EW_SCALE, b, a, scalar=2.0)  # main: b = 2
+    ctx.event_record(0)
+    ctx.stream_select(1)
+    ctx.event_wait(0)
+    ctx.elementwise(N.EW_SCALE, c, b, scalar=3.0)  # side: c = 6
+    ctx.event_record(1)
+    ctx.stream_select(0)
+    ctx.event_wait(1)
+    ctx.elementwise(N.EW_ADD, a, c, b)  # main: a = 8
+    ctx.reserve_sms(0)
+    ctx.sync()
+    assert float(a.min()) == 8.0 and float(a.max()) == 8.0
+    # a single rank's collectives are copies (or nothing, in place)
+    src = torch.arange(1024, device="cuda", dtype=torch.float32)
+    dst = torch.zeros_like(src)
+    ctx.reducescatter(dst, src)
+    ctx.allgather(src, dst)
+    ctx.allreduce(dst)
+    ctx.sync()
+    assert torch.equal(dst, src)
+    with pytest.raises(ValueError):
+        ctx.event_wait(77)  # never recorded
+    with pytest.raises(ValueError):
+        ctx.reserve_sms(10**6)
