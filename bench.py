@@ -181,8 +181,8 @@ def timed_loop(dist: Dist, stream, step, steps: int, warmup: int):
 def gemm_roofline(plan, op_ms, peaks, which):
     """Roofline entry for the dominant kernel of a decoder step: all GEMM launches of one
     step, algorithmic 2MNK flops over their CUDA-event durations."""
-    flops = sum(op.flops() for op in plan.ops if op.kind == "gemm")
-    ms = float(sum(t for op, t in zip(plan.ops, op_ms) if op.kind == "gemm"))
+    flops = sum(op.flops() for op in plan.ops if op.kind in ("gemm", "gemm_rope"))
+    ms = float(sum(t for op, t in zip(plan.ops, op_ms) if op.kind in ("gemm", "gemm_rope")))
     achieved = flops / (ms * 1e-3) / 1e12 if ms > 0 else 0.0
     peak = peaks["bf16_tflops_sustained"]
     share = {}  # with the overlapped schedule the side-stream operators' spans overlap the others'
@@ -193,7 +193,7 @@ def gemm_roofline(plan, op_ms, peaks, which):
     return {
         "bound": "tensor", "kernel": "gemm_bf16_tc_kernel", "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
         "frac": round(achieved / peak, 4), "peak_source": f"{which} cuBLAS bf16, sustained (kernel timed inside a long step)", "traffic": None,
-        "launches_per_step": sum(1 for op in plan.ops if op.kind == "gemm"),
+        "launches_per_step": sum(1 for op in plan.ops if op.kind in ("gemm", "gemm_rope")),
         "step_time_share": {k: round(v / total, 4) for k, v in sorted(share.items())},
     }
 
@@ -396,7 +396,7 @@ def kernel_attention(ctx, peaks, source, causal=False, steps=20, warmup=5) -> di
     achieved = flops / mean_s / 1e12
     return {
         "ms": round(mean_s * 1e3, 5), "tflops": round(achieved, 1), "causal": causal, "shape": [B, H, S, Dh],
-        "roofline": {"bound": "tensor", "kernel": "attn_fwd_tc_kernel", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+        "roofline": {"bound": "tensor", "kernel": "attn_fwd_tc2_kernel", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{source} cuBLAS bf16, burst (kernel timed alone)", "traffic": None},
         "host": (q, k, v, o),
     }

@@ -153,6 +153,18 @@ int lh_b200_gemm(lh_ctx_t* ctx, const lh_memref_t* d, const lh_memref_t* a, cons
                  uint32_t flags);
 
 /*
+ * D = A @ B with the rotary embedding of lh_b200_rope applied to output columns
+ * [0, rope_cols) on the way out: the fused q/k/v projection of the Llama block
+ * (wq, wk, wv followed by apply_rotary_emb, examples/llama/ref_model.py:50-97 and :139-160).
+ * Columns are heads of `head_dim`; row r is position pos0 + (r mod seq). The product is
+ * rounded to D's type before the rotation, as the separate kernels do. bf16 on the
+ * tensor-core kernel rotates in its epilogue from a cached (cos, sin) table; other shapes
+ * run lh_b200_gemm followed by lh_b200_rope.
+ */
+int lh_b200_gemm_rope(lh_ctx_t* ctx, const lh_memref_t* d, const lh_memref_t* a, const lh_memref_t* b,
+                      int rope_cols, int head_dim, int seq, float theta, int pos0);
+
+/*
  * O = softmax(scale . Q K^T [+ causal mask]) V, flash style (never materialises
  * the score matrix). Algorithm of ReplaceWithFusedAttentionOp,
  * lighthouse/dialects/transform/transform_ext/ops/replace_with_fused_attention.py:334-455:
@@ -303,7 +315,8 @@ typedef enum {
   LH_OP_EVENT_RECORD = 13,
   LH_OP_EVENT_WAIT = 14,
   LH_OP_RESERVE_SMS = 15,
-  LH_OP_REDUCE_NORM_GATHER = 16
+  LH_OP_REDUCE_NORM_GATHER = 16,
+  LH_OP_GEMM_ROPE = 17
 } lh_op_kind_t;
 
 /* An operand: a view into a slot. slot < 0 means "absent". */
@@ -334,6 +347,8 @@ typedef struct {
  *   EVENT_RECORD, EVENT_WAIT (none)             i0 = event number
  *   RESERVE_SMS (none)                          i0 = SMs left free by persistent kernels
  *   REDUCE_NORM_GATHER xn, part, h, weight      f0 = eps
+ *   GEMM_ROPE   d, a, b                         i0 = rotary columns, i1 = head size, i2 = sequence
+ *                                               length, f0 = theta, f1 = first position
  */
 typedef struct {
   int32_t kind;

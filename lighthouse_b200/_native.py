@@ -73,7 +73,8 @@ EW_COPY, EW_ADD, EW_MUL, EW_ACT, EW_ADD_ACT, EW_SILU_MUL, EW_SCALE, EW_FILL, EW_
     OP_EVENT_WAIT,
     OP_RESERVE_SMS,
     OP_REDUCE_NORM_GATHER,
-) = range(1, 17)
+    OP_GEMM_ROPE,
+) = range(1, 18)
 
 
 class MemRef(Structure):
@@ -157,6 +158,7 @@ _PROTOTYPES = {
     "lh_b200_comm_destroy": (c_int, [c_void_p]),
     "lh_b200_allreduce": (c_int, [c_void_p, POINTER(MemRef)]),
     "lh_b200_reducescatter": (c_int, [c_void_p, POINTER(MemRef), POINTER(MemRef)]),
+    "lh_b200_gemm_rope": (c_int, [c_void_p, POINTER(MemRef), POINTER(MemRef), POINTER(MemRef), c_int, c_int, c_int, c_float, c_int]),
     "lh_b200_symm_register": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p, POINTER(c_void_p), c_int]),
     "lh_b200_symm_set_flags": (c_int, [c_void_p, c_int, c_int, POINTER(c_void_p)]),
     "lh_b200_symm_clear": (c_int, [c_void_p]),

@@ -151,6 +151,11 @@ class CudaContext:
         rc = self._lib.lh_b200_attention_fwd_noalloc(self.handle, _ref(mo), _ref(mq), _ref(mk), _ref(mv), float(scale), int(bool(causal)))
         N.check(rc, self.handle, "lh_b200_attention_fwd_noalloc")
 
+    def gemm_rope(self, d, a, b, rope_cols: int, head_dim: int, seq: int, theta: float = 10000.0, pos0: int = 0) -> None:
+        md, ma, mb = as_memref(d), as_memref(a), as_memref(b)
+        rc = self._lib.lh_b200_gemm_rope(self.handle, _ref(md), _ref(ma), _ref(mb), int(rope_cols), int(head_dim), int(seq), float(theta), int(pos0))
+        N.check(rc, self.handle, "lh_b200_gemm_rope")
+
     def layernorm(self, out, x, gamma=None, beta=None, eps: float = 1e-5) -> None:
         mo, mx, mg, mb = (as_memref(t) for t in (out, x, gamma, beta))
         N.check(self._lib.lh_b200_layernorm(self.handle, _ref(mo), _ref(mx), _ref(mg), _ref(mb), float(eps)), self.handle, "lh_b200_layernorm")

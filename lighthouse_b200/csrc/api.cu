@@ -201,6 +201,7 @@ extern "C" int lh_b200_ctx_destroy(lh_ctx_t* ctx) {
     if (e) cudaEventDestroy(e);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->symm_counter) cudaFree(ctx->symm_counter);
+  for (auto& t : ctx->rope_tables) cudaFree(t.data);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
   if (ctx->host_status) cudaFreeHost(ctx->host_status);
   delete ctx;
@@ -347,6 +348,34 @@ extern "C" int lh_b200_gemm(lh_ctx_t* ctx, const lh_memref_t* d, const lh_memref
   if (gemm_tc_bf16_supported(ctx, g)) return gemm_tc_bf16_launch(ctx, g);
   if (gemm_tc_tf32x3_supported(ctx, g)) return gemm_tc_tf32x3_launch(ctx, g);
   return gemm_simt_launch(ctx, g);
+}
+
+extern "C" int lh_b200_gemm_rope(lh_ctx_t* ctx, const lh_memref_t* d, const lh_memref_t* a, const lh_memref_t* b,
+                                 int rope_cols, int head_dim, int seq, float theta, int pos0) {
+  if (!ctx) return LH_ERR_INVALID;
+  GemmProblem g;
+  int rc = build_gemm(ctx, g, d, a, b, nullptr, nullptr, nullptr, LH_ACT_NONE, 0);
+  if (rc) return rc;
+  if (head_dim < 2 || head_dim % 2 || seq < 1 || rope_cols < 0 || rope_cols % head_dim || rope_cols > g.N || g.batch != 1 || g.M % seq)
+    return set_error(ctx, LH_ERR_INVALID, "gemm_rope: %d rotary columns of heads of %d, sequence %d, for a %d x %d product", rope_cols, head_dim, seq, g.M, g.N);
+  if (g.M == 0 || g.N == 0) return LH_OK;
+  if (rope_cols > 0 && d->dtype == LH_BF16 && head_dim % 64 == 0 && gemm_tc_bf16_supported(ctx, g)) {
+    rc = rope_table_for(ctx, theta, pos0, seq, head_dim, &g.rope_table);
+    if (rc) return rc;
+    g.rope_cols = rope_cols;
+    g.rope_dim = head_dim;
+    g.rope_seq = seq;
+    return gemm_tc_bf16_launch(ctx, g);
+  }
+  // shapes the fused epilogue does not take: the projection, then the rotary kernel on
+  // its leading columns viewed as (batch, seq, heads, head_dim)
+  rc = lh_b200_gemm(ctx, d, a, b, nullptr, nullptr, nullptr, LH_ACT_NONE, 0);
+  if (rc || rope_cols == 0) return rc;
+  lh_memref_t x = *d;
+  x.rank = 4;
+  x.shape[0] = g.M / seq; x.shape[1] = seq; x.shape[2] = rope_cols / head_dim; x.shape[3] = head_dim;
+  x.strides[0] = seq * d->strides[0]; x.strides[1] = d->strides[0]; x.strides[2] = head_dim * d->strides[1]; x.strides[3] = d->strides[1];
+  return lh_b200_rope(ctx, &x, theta, pos0);
 }
 
 extern "C" int lh_b200_attention_fwd(lh_ctx_t* ctx, const lh_memref_t* o, const lh_memref_t* q, const lh_memref_t* k,
@@ -628,7 +657,7 @@ extern "C" int lh_b200_module_create(lh_ctx_t* ctx, const char* entry_name, cons
   *out = nullptr;
   const int nslots = nargs + ntemps;
   for (int i = 0; i < nops; ++i) {
-    if (ops[i].kind < LH_OP_GEMM || ops[i].kind > LH_OP_REDUCE_NORM_GATHER) return set_error(ctx, LH_ERR_INVALID, "module_create: op %d has unknown kind %d", i, ops[i].kind);
+    if (ops[i].kind < LH_OP_GEMM || ops[i].kind > LH_OP_GEMM_ROPE) return set_error(ctx, LH_ERR_INVALID, "module_create: op %d has unknown kind %d", i, ops[i].kind);
     for (int j = 0; j < LH_MAX_OPERANDS; ++j) {
       const lh_view_t& v = ops[i].operands[j];
       if (v.slot >= nslots) return set_error(ctx, LH_ERR_INVALID, "module_create: op %d operand %d names slot %d of %d", i, j, v.slot, nslots);
@@ -706,6 +735,7 @@ static int run_ops(lh_module* m, void* const* arg_ptrs) {
       case LH_OP_RESERVE_SMS: rc = lh_b200_reserve_sms(ctx, op.i0); break;
       case LH_OP_REDUCE_NORM_GATHER: rc = lh_b200_reduce_norm_gather(ctx, o[0], o[1], o[2], o[3], op.f0); break;
       case LH_OP_ALLGATHER: rc = lh_b200_allgather(ctx, o[0], o[1]); break;
+      case LH_OP_GEMM_ROPE: rc = lh_b200_gemm_rope(ctx, o[0], o[1], o[2], op.i0, op.i1, op.i2, op.f0, static_cast<int>(op.f1)); break;
       default: rc = set_error(ctx, LH_ERR_INVALID, "unknown op kind %d", op.kind);
     }
     if (rc) {

@@ -56,6 +56,9 @@ struct lh_ctx {
   int symm_rank = 0, symm_world = 0;
   uint32_t symm_epoch = 0;            // launches of flag-synchronised kernels so far (same on every rank)
   uint32_t* symm_counter = nullptr;   // device word: blocks finished in the running launch
+  // rotary tables built so far
+  struct RopeTable { float theta; int pos0, seq, dim; float* data; };
+  std::vector<RopeTable> rope_tables;
 };
 
 namespace lh {
@@ -122,6 +125,10 @@ struct GemmProblem {
   const void* R; int r_dtype; int64_t srm, srn, srb;      // added after act (may be null)
   int act;
   uint32_t flags;
+  // rotary embedding applied to output columns [0, rope_cols) in the epilogue (0: none):
+  // heads of rope_dim columns, position = row mod rope_seq; rope_table[pos][pair] = (cos, sin)
+  int rope_cols = 0, rope_dim = 0, rope_seq = 0;
+  const float* rope_table = nullptr;
 };
 
 // Epilogue parameters passed by value to the kernels.
@@ -132,6 +139,7 @@ struct EpiParams {
   const void* R; int r_dtype; int64_t ldr;
   int act;
   int swiglu;
+  const float* rope_table; int rope_cols, rope_dim, rope_seq;
 };
 
 int gemm_tc_bf16_supported(const lh_ctx* ctx, const GemmProblem& p);
@@ -162,6 +170,8 @@ int layernorm_launch(lh_ctx* ctx, const lh_memref_t* out, const lh_memref_t* x, 
                      const lh_memref_t* beta, float eps, int rms);
 int softmax_launch(lh_ctx* ctx, const lh_memref_t* out, const lh_memref_t* x);
 int rope_launch(lh_ctx* ctx, const lh_memref_t* x, float theta, int pos0);
+// (cos, sin) of every (position, pair) for rope_launch's arithmetic, cached per context.
+int rope_table_for(lh_ctx* ctx, float theta, int pos0, int seq, int dim, const float** table);
 int elementwise_launch(lh_ctx* ctx, int kind, const lh_memref_t* out, const lh_memref_t* a,
                        const lh_memref_t* b, int act, float scalar);
 int embedding_launch(lh_ctx* ctx, const lh_memref_t* out, const lh_memref_t* ids, const lh_memref_t* wte,

@@ -346,6 +346,24 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           activate_block(v, e.act);
           if (use_r) add_row_segment<OUT_F32>(v, rseg);
+          if (!OUT_F32 && col0 < e.rope_cols) {
+            // Rotary embedding on the way out: pairs (2i, 2i+1) of a head are neighbours in
+            // this thread's registers. The value is first rounded to the output type, as a
+            // separate rotary kernel reading the stored projection would see it.
+            const int pos = row_ok ? row % e.rope_seq : 0;
+            const float4* tab = reinterpret_cast<const float4*>(e.rope_table) +
+                                (static_cast<int64_t>(pos) * (e.rope_dim / 2) + (col0 % e.rope_dim) / 2) / 2;
+#pragma unroll
+            for (int j = 0; j < CHUNK / 4; ++j) {
+              const float4 cs = __ldg(tab + j);  // (cos, sin) of two pairs
+              const float x0 = __bfloat162float(__float2bfloat16_rn(v[4 * j])), x1 = __bfloat162float(__float2bfloat16_rn(v[4 * j + 1]));
+              const float x2 = __bfloat162float(__float2bfloat16_rn(v[4 * j + 2])), x3 = __bfloat162float(__float2bfloat16_rn(v[4 * j + 3]));
+              v[4 * j] = x0 * cs.x - x1 * cs.y;
+              v[4 * j + 1] = x0 * cs.y + x1 * cs.x;
+              v[4 * j + 2] = x2 * cs.z - x3 * cs.w;
+              v[4 * j + 3] = x2 * cs.w + x3 * cs.z;
+            }
+          }
         }
         uint8_t* sb = stage_bufs + sbuf * STAGING_BUF_BYTES;
         if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer is done
@@ -529,6 +547,7 @@ int gemm_tc_bf16_launch(lh_ctx* ctx, const GemmProblem& p) {
   epi.C = p.C; epi.c_dtype = p.c_dtype; epi.ldc = p.scm;
   epi.bias = p.bias; epi.bias_dtype = p.bias_dtype;
   epi.R = p.R; epi.r_dtype = p.r_dtype; epi.ldr = p.srm;
+  epi.rope_table = p.rope_table; epi.rope_cols = p.rope_table ? p.rope_cols : 0; epi.rope_dim = p.rope_dim; epi.rope_seq = p.rope_seq;
   epi.act = p.act;
   epi.swiglu = (p.flags & LH_GEMM_SWIGLU) ? 1 : 0;
   const bool b_kmajor = (p.sbk == 1 && p.N > 1 && p.sbn >= p.K);

@@ -327,6 +327,20 @@ __global__ void __launch_bounds__(256) rope_kernel(const RopeParams p) {
   }
 }
 
+// Table of (cos, sin) per (position, pair), with exactly rope_kernel's arithmetic, for the
+// GEMM epilogue that rotates q and k columns on their way out.
+__global__ void __launch_bounds__(256) rope_table_kernel(float2* table, int seq, int dim, float theta, int pos0) {
+  const int half = dim / 2;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= seq * half) return;
+  const int i = idx % half, s = idx / half;
+  const float freq = 1.0f / powf(theta, static_cast<float>(2 * i) / static_cast<float>(dim));
+  const float ang = static_cast<float>(pos0 + s) * freq;
+  float sn, cs;
+  sincosf(ang, &sn, &cs);
+  table[idx] = make_float2(cs, sn);
+}
+
 // -------------------------------------------------------------- elementwise
 struct EwParams {
   int kind, act;
@@ -452,6 +466,24 @@ int rope_launch(lh_ctx* ctx, const lh_memref_t* x, float theta, int pos0) {
   const int64_t total = static_cast<int64_t>(p.S) * (p.D / 2);
   rope_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(p);
   LH_CHECK_LAUNCH(ctx, "rope_kernel");
+  return LH_OK;
+}
+
+int rope_table_for(lh_ctx* ctx, float theta, int pos0, int seq, int dim, const float** table) {
+  for (const auto& t : ctx->rope_tables)
+    if (t.theta == theta && t.pos0 == pos0 && t.seq == seq && t.dim == dim) {
+      *table = t.data;
+      return LH_OK;
+    }
+  if (seq < 1 || dim < 2 || dim % 2) return set_error(ctx, LH_ERR_INVALID, "rope table: seq %d, head size %d", seq, dim);
+  void* mem = nullptr;
+  const int n = seq * (dim / 2);
+  int rc = lh_b200_malloc(ctx, static_cast<size_t>(n) * sizeof(float2), &mem);
+  if (rc) return rc;
+  rope_table_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>(static_cast<float2*>(mem), seq, dim, theta, pos0);
+  LH_CHECK_LAUNCH(ctx, "rope_table_kernel");
+  ctx->rope_tables.push_back({theta, pos0, seq, dim, static_cast<float*>(mem)});
+  *table = static_cast<float*>(mem);
   return LH_OK;
 }
 

@@ -153,7 +153,7 @@ class PlanOp:
     def flops(self) -> int:
         """Algorithmic flops with the reference's conventions (examples/xegpu/matmul.py:52-64,
         examples/xegpu/fused_attention.py:38-43)."""
-        if self.kind == "gemm":
+        if self.kind in ("gemm", "gemm_rope"):
             a, b = self.operands[1], self.operands[2]
             batch = a.shape[0] if a.rank == 3 else 1
             return 2 * batch * a.shape[-2] * a.shape[-1] * b.shape[-1]
@@ -181,6 +181,7 @@ _KIND_CODES = {
     "event_wait": N.OP_EVENT_WAIT,
     "reserve_sms": N.OP_RESERVE_SMS,
     "reduce_norm_gather": N.OP_REDUCE_NORM_GATHER,
+    "gemm_rope": N.OP_GEMM_ROPE,
 }
 
 
@@ -255,6 +256,12 @@ class Plan:
         self.ops.append(PlanOp("reducescatter", [out, inp]))
         return out
 
+    def gemm_rope(self, d, a, b, rope_cols: int, head_dim: int, seq: int, theta: float = 10000.0, pos0: int = 0):
+        """``d = a @ b`` with the rotary embedding applied to its first ``rope_cols`` columns
+        (heads of ``head_dim``; row r is position ``pos0 + r mod seq``)."""
+        self.ops.append(PlanOp("gemm_rope", [d, a, b], {"rope_cols": int(rope_cols), "head_dim": int(head_dim), "seq": int(seq), "theta": float(theta), "pos0": int(pos0)}))
+        return d
+
     def reduce_norm_gather(self, xn, part, h, weight, eps: float):
         """Fused reduce-scatter + residual add + RMSNorm + all-gather over symmetric memory:
         ``h += sum over ranks of part[my rows]`` (skipped when ``part`` is None), then
@@ -320,6 +327,8 @@ class Plan:
                 o.i0, o.i1, o.f0 = EW_CODES[at["ew"]], ACT_CODES[at.get("act", "none")], at.get("scalar", 0.0)
             elif op.kind == "embedding":
                 o.i0 = at.get("period", 0)
+            elif op.kind == "gemm_rope":
+                o.i0, o.i1, o.i2, o.f0, o.f1 = at["rope_cols"], at["head_dim"], at["seq"], at["theta"], float(at["pos0"])
             elif op.kind in ("stream", "event_record", "event_wait", "reserve_sms"):
                 o.i0 = at["index"]
         return sig, nargs, temps, len(self.temp_bytes), ops, len(self.ops)

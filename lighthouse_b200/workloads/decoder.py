@@ -251,9 +251,9 @@ def build_llama_plan(cfg: LlamaConfig, rank: int = 0, tp: int = 1, name: str = "
     for li in range(cfg.n_layer):
         a = {k: p.arg(2 + li * len(LLAMA_LAYER_KEYS) + i) for i, k in enumerate(LLAMA_LAYER_KEYS)}
         p.rmsnorm(hn, h, a["attention_norm"], cfg.eps)
-        p.gemm(qkv, hn, a["wqkv"].t())
+        # q and k heads are the leading columns of the packed projection: rotated in its epilogue
+        p.gemm_rope(qkv, hn, a["wqkv"].t(), ql + kl, hd, cfg.seq, cfg.theta, 0)
         q, k, v = bshd(qkv, 0, hq), bshd(qkv, ql, hkv), bshd(qkv, ql + kl, hkv)
-        p.rope(bshd(qkv, 0, hq + hkv), cfg.theta, 0)  # q and k heads are adjacent columns: one launch
         to_bhsd = lambda z: z.permute((0, 2, 1, 3))
         p.attention(to_bhsd(bshd(att, 0, hq)), to_bhsd(q), to_bhsd(k), to_bhsd(v), 1.0 / math.sqrt(hd), True)
         p.gemm(h, att, a["wo"].t(), residual=h if first else None)
@@ -386,9 +386,9 @@ def build_llama_plan_overlapped(cfg: LlamaConfig, rank: int, tp: int, microbatch
         a = layer_args(li)
         for mb in range(m):
             p.event_wait(chain.ready[mb])
-            p.gemm(qkv[mb], xn[mb], a["wqkv"].t())
+            # q and k heads are the leading columns of the packed projection: rotated in its epilogue
+            p.gemm_rope(qkv[mb], xn[mb], a["wqkv"].t(), ql + kl, hd, cfg.seq, cfg.theta, 0)
             q, k, v = bshd(qkv[mb], 0, hq), bshd(qkv[mb], ql, hkv), bshd(qkv[mb], ql + kl, hkv)
-            p.rope(bshd(qkv[mb], 0, hq + hkv), cfg.theta, 0)  # q and k heads are adjacent columns: one launch
             p.attention(to_bhsd(bshd(att[mb], 0, hq)), to_bhsd(q), to_bhsd(k), to_bhsd(v), 1.0 / math.sqrt(hd), True)
             p.gemm(part[mb], att[mb], a["wo"].t())
             chain.fork()

@@ -83,6 +83,16 @@ class CpuPlanRunner:
             acc = acc + self.read(res).astype(np.float32)
         self.write(d, acc)
 
+    def _gemm_rope(self, op):
+        d, a, b = op.operands[:3]
+        at = op.attrs
+        acc = R.round_to(self.read(a).astype(np.float32) @ self.read(b).astype(np.float32), d.dtype)
+        cols, hd, seq = at["rope_cols"], at["head_dim"], at["seq"]
+        if cols:
+            x = acc[:, :cols].reshape(acc.shape[0] // seq, seq, cols // hd, hd)
+            acc[:, :cols] = R.rope(x, at["theta"], at["pos0"], d.dtype).reshape(acc.shape[0], cols)
+        self.write(d, acc)
+
     def _attention(self, op):
         o, q, k, v = op.operands[:4]
         Q, K, V = self.read(q), self.read(k), self.read(v)
@@ -169,7 +179,7 @@ class CpuPlanRunner:
     # The interpreter runs both streams in program order, which every correctly synchronised
     # plan allows, and checks the synchronisation itself with vector clocks: two accesses to
     # one slot from different streams, at least one of them a write, must be ordered by events.
-    _WRITES = {"gemm": 1, "attention": 1, "layernorm": 1, "rmsnorm": 1, "softmax": 1, "rope": 1, "elementwise": 1,
+    _WRITES = {"gemm": 1, "gemm_rope": 1, "attention": 1, "layernorm": 1, "rmsnorm": 1, "softmax": 1, "rope": 1, "elementwise": 1,
                "embedding": 1, "allreduce": 1, "allgather": 1, "reducescatter": 1, "reduce_norm_gather": 1}
 
     def _reset_clocks(self):

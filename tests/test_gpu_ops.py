@@ -327,3 +327,25 @@ def test_side_stream_events_and_collectives_of_one_rank(ctx):
         ctx.event_wait(77)  # never recorded
     with pytest.raises(ValueError):
         ctx.reserve_sms(10**6)
+
+
+@pytest.mark.parametrize("m,n,k,cols,hd,seq", [(256, 768, 512, 640, 128, 128), (384, 320, 256, 256, 64, 96), (64, 48, 32, 32, 16, 32)])
+def test_gemm_with_rotary_epilogue(ctx, m, n, k, cols, hd, seq):
+    """Projection + rotary embedding of its leading columns in one call: the tensor-core
+    epilogue (head sizes that are multiples of 64) and the two-kernel form (the rest) against
+    the oracle's product -> round -> rotate."""
+    rng = np.random.RandomState(m + n)
+    a, b = R.round_bf16(rng.randn(m, k).astype(np.float32) * 0.5), R.round_bf16(rng.randn(k, n).astype(np.float32) * 0.2)
+    d = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    ctx.gemm_rope(d, dev(a, torch.bfloat16), dev(b, torch.bfloat16), cols, hd, seq, 10000.0, 3)
+    ctx.sync()
+    want = R.round_bf16(a @ b)
+    want[:, :cols] = R.rope(want[:, :cols].reshape(m // seq, seq, cols // hd, hd), 10000.0, 3, "bf16").reshape(m, cols)
+    assert max_rel_err(host(d), want) <= TOL_BF16
+    # untouched columns are the plain product
+    plain = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    ctx.gemm(plain, dev(a, torch.bfloat16), dev(b, torch.bfloat16))
+    ctx.sync()
+    assert torch.equal(plain[:, cols:], d[:, cols:])
+    with pytest.raises(ValueError):
+        ctx.gemm_rope(d, dev(a, torch.bfloat16), dev(b, torch.bfloat16), cols + 1, hd, seq)
