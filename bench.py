@@ -561,7 +561,7 @@ def main() -> int:
     ap.add_argument("--microbatches", type=int, default=2, help="tensor parallel only: micro-batches whose collectives overlap each other's compute (0: one synchronous all-reduce per contraction)")
     ap.add_argument("--collectives", choices=["fused", "nccl"], default="fused", help="tensor parallel with micro-batches: one multimem kernel per reduce+norm+gather, or NCCL reduce-scatter / all-gather around row kernels")
     ap.add_argument("--timeline", default="", help="decoder workloads: write rank 0's per-operator timeline of the last timed step to this file")
-    ap.add_argument("--reserve-sms", type=int, default=16, help="SMs the persistent GEMMs leave to the collectives in the overlapped schedule")
+    ap.add_argument("--reserve-sms", type=int, default=8, help="SMs the persistent GEMMs leave to the collectives in the overlapped schedule")
     ap.add_argument("--no-kernels", action="store_true", help="skip the GEMM / attention kernel lines of the decoder workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
