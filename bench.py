@@ -374,6 +374,29 @@ def kernel_gemm(ctx, peaks, source, K=4096, steps=20, warmup=5) -> dict:
     }
 
 
+def kernel_gemm_f32(ctx, steps=20, warmup=5) -> dict:
+    """f32 GEMM accumulating into C, M = N = K = 1024, A, B ~ U(-1, 1) (config 1): the lh-run
+    matmul. Runs as 3 x TF32 on the tensor cores (two operand-split launches + one tcgen05
+    GEMM over 3K); the flop count is the f32 problem's 2MNK."""
+    import torch
+
+    from lighthouse_b200.plan import ArgSpec, Plan
+    from lighthouse_b200.workloads import synthetic as I
+    from lighthouse_b200.workloads.session import PlanSession
+
+    M = N = K = 1024
+    a, b, c = I.gemm_f32_uniform(M, N, K, seed=1)
+    plan = Plan("matmul_f32", [ArgSpec((M, K), "f32", "a"), ArgSpec((K, N), "f32", "b"), ArgSpec((M, N), "f32", "c")])
+    plan.gemm(plan.arg(2), plan.arg(0), plan.arg(1), c=plan.arg(2))
+    sess = PlanSession(plan, ctx=ctx)
+    dev_args = [torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda(), torch.from_numpy(c).cuda()]
+    times = sess.benchmark(dev_args, nruns=steps, nwarmup=warmup, l2_flush_bytes=L2_FLUSH_BYTES)
+    sess.close()
+    mean_s = float(times.mean())
+    return {"ms": round(mean_s * 1e3, 5), "best_ms": round(float(times.min()) * 1e3, 5), "tflops": round(2.0 * M * N * K / mean_s / 1e12, 2), "shape": [M, N, K],
+            "path": "3xTF32 tcgen05 (split A, split B, GEMM over 3K); f32 result within 1e-5 of the loop nest"}
+
+
 def kernel_attention(ctx, peaks, source, causal=False, steps=20, warmup=5) -> dict:
     """Flash attention forward, B8 H16 S2048 D128 bf16 (config 3)."""
     import torch
@@ -585,6 +608,7 @@ def main() -> int:
             g = kernel_gemm(ctx, peaks, source)
             g.pop("host")
             kernels["gemm_bias_relu_4096x4096x4096"] = g
+            kernels["gemm_f32_1024x1024x1024"] = kernel_gemm_f32(ctx)
             for causal in (False, True):
                 a = kernel_attention(ctx, peaks, source, causal=causal)
                 a.pop("host")

@@ -154,7 +154,10 @@ __device__ __forceinline__ void load_row_segment(uint4 (&seg)[8], const void* ba
   }
 }
 
-template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32>
+// TF32: the operands are f32 arrays read as tf32 (kind::tf32, K = 8 per instruction, 32
+// elements per 128-byte swizzle row); everything else - ring, tensor memory, epilogue - is the
+// bf16 kernel's.
+template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, bool TF32 = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmD, const GemmTcParams p) {
@@ -173,6 +176,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+  constexpr int BKE = TF32 ? BK / 2 : BK;  // elements per k-block (always 128 bytes)
+  static_assert(!TF32 || (B_KMAJOR && OUT_F32), "the tf32 variant takes k-major B and writes f32");
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -215,9 +220,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           uint8_t* sA = smem + stage * L::STAGE_BYTES;
           uint8_t* sB = sA + A_TILE_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
-          tma_load_2d(sA, &tmA, &full_bar[stage], kb * BK, m_blk * BM);
+          tma_load_2d(sA, &tmA, &full_bar[stage], kb * BKE, m_blk * BM);
           if (B_KMAJOR) {
-            tma_load_2d(sB, &tmB, &full_bar[stage], kb * BK, n_blk * BN);
+            tma_load_2d(sB, &tmB, &full_bar[stage], kb * BKE, n_blk * BN);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
@@ -233,7 +238,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(UMMA_BF16, BM, BN, false, !B_KMAJOR);
+      constexpr uint32_t idesc = make_idesc(TF32 ? UMMA_TF32 : UMMA_BF16, BM, BN, false, !B_KMAJOR);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -257,7 +262,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint64_t adesc = make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
             const uint64_t bdesc = B_KMAJOR ? make_smem_desc_sw128(b_addr + k * 32, 16, 1024)
                                             : make_smem_desc_sw128(b_addr + k * 2048, 64 * BK * 2, 1024);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (TF32) umma_tf32_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == STAGES) {
@@ -410,23 +416,26 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
-template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32>
+template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, bool TF32 = false>
 int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi) {
   using L = SmemLayout<BN, STAGES>;
   CUtensorMap tmA, tmB, tmD;
   const int n_out = epi.swiglu ? pr.N / 2 : pr.N;
+  constexpr uint32_t BKE = TF32 ? BK / 2 : BK;
+  constexpr uint64_t ab_size = TF32 ? 4 : 2;
+  constexpr int ab_dtype = TF32 ? LH_F32 : LH_BF16;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(pr.K), static_cast<uint64_t>(pr.M)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(pr.sam) * 2};
-    const uint32_t box[2] = {BK, BM};
-    int rc = encode_tensor_map(ctx, &tmA, LH_BF16, 2, const_cast<void*>(pr.A), dims, strides, box, 1);
+    const uint64_t strides[1] = {static_cast<uint64_t>(pr.sam) * ab_size};
+    const uint32_t box[2] = {BKE, BM};
+    int rc = encode_tensor_map(ctx, &tmA, ab_dtype, 2, const_cast<void*>(pr.A), dims, strides, box, 1);
     if (rc) return rc;
   }
   if (B_KMAJOR) {  // B(k,n) with unit k stride: a row-major (N,K) array
     const uint64_t dims[2] = {static_cast<uint64_t>(pr.K), static_cast<uint64_t>(pr.N)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(pr.sbn) * 2};
-    const uint32_t box[2] = {BK, BN};
-    int rc = encode_tensor_map(ctx, &tmB, LH_BF16, 2, const_cast<void*>(pr.B), dims, strides, box, 1);
+    const uint64_t strides[1] = {static_cast<uint64_t>(pr.sbn) * ab_size};
+    const uint32_t box[2] = {BKE, BN};
+    int rc = encode_tensor_map(ctx, &tmB, ab_dtype, 2, const_cast<void*>(pr.B), dims, strides, box, 1);
     if (rc) return rc;
   } else {  // B(k,n) with unit n stride: a row-major (K,N) array
     const uint64_t dims[2] = {static_cast<uint64_t>(pr.N), static_cast<uint64_t>(pr.K)};
@@ -450,10 +459,10 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi) {
   p.n_out = n_out;
   p.num_m_blocks = (pr.M + BM - 1) / BM;
   p.num_n_blocks = (pr.N + BN - 1) / BN;
-  p.num_k_blocks = (pr.K + BK - 1) / BK;
+  p.num_k_blocks = (pr.K + static_cast<int>(BKE) - 1) / static_cast<int>(BKE);
   p.epi = epi;
   p.dev_status = ctx->dev_status;
-  auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES, OUT_F32>;
+  auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES, OUT_F32, TF32>;
   LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
   // A persistent grid that fills the GPU would make side-stream kernels (collectives) wait for
@@ -557,9 +566,121 @@ int gemm_tc_bf16_launch(lh_ctx* ctx, const GemmProblem& p) {
   return out_f32 ? launch_bn<false, true>(ctx, p, epi, bn) : launch_bn<false, false>(ctx, p, epi, bn);
 }
 
-int gemm_tc_tf32x3_supported(const lh_ctx*, const GemmProblem&) { return 0; }
-int gemm_tc_tf32x3_launch(lh_ctx* ctx, const GemmProblem&) {
-  return set_error(ctx, LH_ERR_UNSUPPORTED, "3xTF32 tensor-core GEMM is not built");
+// ------------------------------------------------------------------ f32 GEMM as 3 x TF32
+// tf32 keeps 10 mantissa bits, so one tf32 product is not an f32 product. Each operand is
+// split into a tf32-exact head and the (f32-exact) remainder, hi = x with the low 13 mantissa
+// bits cleared, lo = x - hi, and the product is summed as hi*hi + lo*hi + hi*lo with f32
+// accumulation in tensor memory: the dropped lo*lo term and the truncation of lo are ~2^-21
+// relative. The three partial products are one tf32 GEMM over a concatenated k dimension:
+//   A' (M, 3K) = [A_hi | A_lo | A_hi],   B' (N, 3K) = [B_hi | B_hi | B_lo]  (both k-major)
+// written by split_tf32_kernel into context scratch (which also transposes B as needed).
+// The tensor core adds into its f32 accumulator with truncation, a bias towards zero of about
+// 3e-8 of the sum per instruction (measured: 1.2e-5 over the 375 instructions of K = 1000). So
+// k is cut into segments of TF32X3_SEGMENT: each segment is one launch whose epilogue adds
+// the running result as C with a correctly rounded f32 add, and the concatenation above is
+// per segment.
+namespace {
+
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict__ src, int64_t s_row, int64_t s_k, int rows, int K,
+                                                         float* __restrict__ dst, int64_t ld, int lo_slot, int seg) {
+  // 32 rows x 32 k per block through shared memory, so that both the read (along whichever of
+  // row / k is contiguous in src) and the write (along k) are coalesced.
+  __shared__ float tile[32][33];
+  const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const bool k_contig = (s_k == 1);
+  for (int i = ty; i < 32; i += 8) {
+    const int r = k_contig ? r0 + i : r0 + tx;
+    const int k = k_contig ? k0 + tx : k0 + i;
+    const float v = (r < rows && k < K) ? src[r * s_row + k * s_k] : 0.f;
+    if (k_contig) tile[i][tx] = v;
+    else tile[tx][i] = v;
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int r = r0 + i, k = k0 + tx;
+    if (r < rows && k < K) {
+      const float x = tile[i][tx];
+      const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+      const float lo = x - hi;
+      // k belongs to segment k / seg, which owns columns [3 * first, 3 * (first + len)) as
+      // three slots of len; the remainder sits in slot lo_slot, the head in the other two
+      const int first = (k / seg) * seg;
+      const int len = min(seg, K - first);
+      float* out = dst + r * ld + 3 * static_cast<int64_t>(first) + (k - first);
+      out[0] = lo_slot == 0 ? lo : hi;
+      out[len] = lo_slot == 1 ? lo : hi;
+      out[2 * len] = lo_slot == 2 ? lo : hi;
+    }
+  }
+}
+
+constexpr int TF32X3_SEGMENT = 256;                   // original k per launch: 96 tf32 instructions per accumulator
+constexpr int64_t TF32X3_MIN_WORK = 1ll << 21;        // below this the CUDA-core kernel's single launch wins
+constexpr size_t TF32X3_MAX_SCRATCH = 3ull << 30;     // split copies larger than this stay on the CUDA cores
+
+inline int64_t tf32x3_ld(int K) { return (3ll * K + 3) & ~3ll; }  // rows 16-byte aligned
+
+}  // namespace
+
+int gemm_tc_tf32x3_supported(const lh_ctx* ctx, const GemmProblem& p) {
+  if (ctx->cc_major != 10) return 0;
+  if (p.flags & (LH_GEMM_FORCE_SIMT | LH_GEMM_SWIGLU)) return 0;
+  if (p.batch != 1) return 0;
+  if (p.a_dtype != LH_F32 || p.b_dtype != LH_F32 || p.d_dtype != LH_F32) return 0;
+  if (p.M < 1 || p.K < 1 || p.N < 8 || p.N % 8) return 0;
+  if (static_cast<int64_t>(p.M) * p.N * p.K < TF32X3_MIN_WORK) return 0;
+  const size_t scratch = static_cast<size_t>(tf32x3_ld(p.K)) * 4 * (static_cast<size_t>(p.M) + p.N);
+  if (scratch > TF32X3_MAX_SCRATCH) return 0;
+  auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+  if (p.sdn != 1 || (p.sdm % 4) != 0 || p.sdm < p.N || !aligned16(p.D)) return 0;
+  if (p.C && (p.c_dtype != LH_F32 || p.scn != 1 || (p.scm % 4) != 0 || !aligned16(p.C))) return 0;
+  if (p.R && (p.r_dtype != LH_F32 || p.srn != 1 || (p.srm % 4) != 0 || !aligned16(p.R))) return 0;
+  if (p.bias && ((p.bias_dtype != LH_BF16 && p.bias_dtype != LH_F32) || !aligned16(p.bias))) return 0;
+  return 1;
+}
+
+int gemm_tc_tf32x3_launch(lh_ctx* ctx, const GemmProblem& p) {
+  const int64_t ld = tf32x3_ld(p.K);
+  const size_t a_bytes = static_cast<size_t>(p.M) * ld * 4, b_bytes = static_cast<size_t>(p.N) * ld * 4;
+  const size_t a_pad = (a_bytes + 255) & ~static_cast<size_t>(255);
+  int rc = ensure_scratch(ctx, a_pad + b_bytes);
+  if (rc) return rc;
+  float* a3 = static_cast<float*>(ctx->scratch);
+  float* b3 = reinterpret_cast<float*>(static_cast<char*>(ctx->scratch) + a_pad);
+  const dim3 ga((p.K + 31) / 32, (p.M + 31) / 32), gb((p.K + 31) / 32, (p.N + 31) / 32);
+  split_tf32_kernel<<<ga, 256, 0, ctx->stream>>>(static_cast<const float*>(p.A), p.sam, p.sak, p.M, p.K, a3, ld, 1, TF32X3_SEGMENT);
+  LH_CHECK_LAUNCH(ctx, "split_tf32_kernel");
+  split_tf32_kernel<<<gb, 256, 0, ctx->stream>>>(static_cast<const float*>(p.B), p.sbn, p.sbk, p.N, p.K, b3, ld, 2, TF32X3_SEGMENT);
+  LH_CHECK_LAUNCH(ctx, "split_tf32_kernel");
+  // tile width by the same wave model as the bf16 kernel, between the two instantiated widths
+  const int sms = ctx->sm_count - ctx->reserved_sms > 0 ? ctx->sm_count - ctx->reserved_sms : 1;
+  const int64_t num_m = (p.M + BM - 1) / BM;
+  const int64_t w256 = (num_m * ((p.N + 255) / 256) + sms - 1) / sms, w128 = (num_m * ((p.N + 127) / 128) + sms - 1) / sms;
+  const bool wide = w256 * 256 <= w128 * 128 / 0.72;
+  const int nseg = (p.K + TF32X3_SEGMENT - 1) / TF32X3_SEGMENT;
+  for (int sgm = 0; sgm < nseg; ++sgm) {
+    const int first = sgm * TF32X3_SEGMENT;
+    const int len = p.K - first < TF32X3_SEGMENT ? p.K - first : TF32X3_SEGMENT;
+    const bool is_first = sgm == 0, is_last = sgm == nseg - 1;
+    GemmProblem q = p;
+    q.K = 3 * len;
+    q.A = a3 + 3 * static_cast<int64_t>(first); q.sam = ld; q.sak = 1;
+    q.B = b3 + 3 * static_cast<int64_t>(first); q.sbn = ld; q.sbk = 1;
+    EpiParams epi;
+    epi.D = p.D; epi.d_dtype = p.d_dtype; epi.ldd = p.sdm;
+    // the caller's C enters with the first segment, the running sum (D) with the later ones;
+    // bias, activation and residual belong to the last
+    epi.C = is_first ? p.C : p.D; epi.c_dtype = LH_F32; epi.ldc = is_first ? p.scm : p.sdm;
+    epi.bias = is_last ? p.bias : nullptr; epi.bias_dtype = p.bias_dtype;
+    epi.R = is_last ? p.R : nullptr; epi.r_dtype = p.r_dtype; epi.ldr = p.srm;
+    epi.act = is_last ? p.act : LH_ACT_NONE;
+    epi.swiglu = 0;
+    epi.rope_table = nullptr; epi.rope_cols = 0; epi.rope_dim = 0; epi.rope_seq = 0;
+    rc = wide ? launch_variant<256, true, 4, true, true>(ctx, q, epi) : launch_variant<128, true, 6, true, true>(ctx, q, epi);
+    if (rc) return rc;
+  }
+  return LH_OK;
 }
 
 }  // namespace lh

@@ -42,6 +42,36 @@ def test_gemm_f32_matches_loop_nest(ctx, shape):
     assert max_rel_err(host(d), ref) <= TOL_F32
 
 
+@pytest.mark.parametrize("shape", [(300, 264, 77), (129, 512, 1000), (2048, 128, 9)])
+def test_gemm_f32_tensor_core_split_path(ctx, shape):
+    """Shapes large enough for the 3 x TF32 tensor-core path (N a multiple of 8), ragged in M
+    and K, accumulating into C, with bias, activation and residual, and with transposed
+    operand views: within the f32 tolerance of the loop nest."""
+    m, n, k = shape
+    a, b, _ = I.gemm_f32_uniform(m, n, k, seed=m + k)
+    c = np.random.RandomState(2).rand(m, n).astype(np.float32)
+    ref = oracle_build.matmul_loops(a, b, c)
+    d = dev(c.copy())
+    ctx.gemm(d, dev(a), dev(b), c=d)
+    ctx.sync()
+    assert max_rel_err(host(d), ref) <= TOL_F32
+    d2 = dev(c.copy())
+    ctx.gemm(d2, dev(np.ascontiguousarray(a.T)).t(), dev(np.ascontiguousarray(b.T)).t(), c=d2)
+    ctx.sync()
+    assert max_rel_err(host(d2), ref) <= TOL_F32
+    bias, res = np.random.RandomState(3).randn(n).astype(np.float32), np.random.RandomState(4).randn(m, n).astype(np.float32)
+    d3 = torch.zeros(m, n, device="cuda")
+    ctx.gemm(d3, dev(a), dev(b), bias=dev(bias), residual=dev(res), act=N.ACT_RELU)
+    ctx.sync()
+    want = np.maximum(oracle_build.matmul_loops(a, b, np.zeros((m, n), np.float32)) + bias, 0) + res
+    assert max_rel_err(host(d3), want) <= TOL_F32
+    # the CUDA-core kernel on request, same answer
+    d4 = dev(c.copy())
+    ctx.gemm(d4, dev(a), dev(b), c=d4, flags=N.GEMM_FORCE_SIMT)
+    ctx.sync()
+    assert max_rel_err(host(d4), host(d)) <= TOL_F32
+
+
 def test_gemm_f32_config1_full_size(ctx):
     """Config 1: 1024^3, A, B ~ U(-1, 1), zero C; the C loop-nest oracle is the reference."""
     a, b, c = I.gemm_f32_uniform(1024, 1024, 1024, seed=1)
