@@ -32,13 +32,28 @@ __device__ __forceinline__ void store_from_f32(void* p, int dtype, int64_t idx, 
   }
 }
 
+// erf by Abramowitz & Stegun 7.1.26 (|error| <= 1.5e-7, two special-function instructions and
+// a short polynomial, no branches): an epilogue applies it to every element of a tile, where
+// the library erff's length and divergent ranges cost more than the tile's main loop.
+__device__ __forceinline__ float erf_as(float z) {
+  const float a = fabsf(z);
+  const float t = __fdividef(1.f, fmaf(0.3275911f, a, 1.f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float r = 1.f - poly * t * __expf(-a * a);
+  return copysignf(r, z);
+}
+
 __device__ __forceinline__ float apply_act(float x, int act) {
   switch (act) {
     case LH_ACT_RELU: return fmaxf(x, 0.f);
-    case LH_ACT_GELU_ERF: return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
+    case LH_ACT_GELU_ERF: return 0.5f * x * (1.f + erf_as(x * 0.70710678118654752440f));
     case LH_ACT_GELU_TANH: {
+      // 0.5 x (1 + tanh u) = x / (1 + exp(-2u))
       const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-      return 0.5f * x * (1.f + tanhf(u));
+      return __fdividef(x, 1.f + __expf(-2.f * u));
     }
     case LH_ACT_SILU: return x / (1.f + __expf(-x));
     case LH_ACT_SIGMOID: return 1.f / (1.f + __expf(-x));

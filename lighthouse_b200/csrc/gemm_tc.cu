@@ -298,6 +298,28 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int out_cols = e.swiglu ? BN / 2 : BN;
       const int out_col_base = n_blk * out_cols;
       const int units = out_cols / CHUNK;
+      // The tile's bias, 8 columns per lane, fetched once per tile with one coalesced load and
+      // handed round by shuffles (a per-unit load by every lane of the same address costs an L2
+      // round trip per group of 8 columns).
+      float bq[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (e.bias && lane * 8 < out_cols && out_col_base + lane * 8 < p.n_out) {
+        const int bc = out_col_base + lane * 8;
+        if (e.bias_dtype == LH_BF16) {
+          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(e.bias) + bc));
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h2[i]);
+            bq[2 * i] = f.x;
+            bq[2 * i + 1] = f.y;
+          }
+        } else {
+          const float4 b0 = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(e.bias) + bc));
+          const float4 b1 = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(e.bias) + bc + 4));
+          bq[0] = b0.x; bq[1] = b0.y; bq[2] = b0.z; bq[3] = b0.w;
+          bq[4] = b1.x; bq[5] = b1.y; bq[6] = b1.z; bq[7] = b1.w;
+        }
+      }
 #pragma unroll 1
       for (int u = 0; u < units; ++u) {
         const int col0 = out_col_base + u * CHUNK;
@@ -340,14 +362,12 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!e.swiglu) {
           if (use_c) add_row_segment<OUT_F32>(v, cseg);
           if (e.bias) {
+            // lane (u * CHUNK) / 8 + g holds the bias of this unit's g-th group of 8 columns
 #pragma unroll
             for (int g = 0; g < CHUNK / 8; ++g) {
-              if (col0 + g * 8 < p.n_out) {
-                float bv[8];
-                load8_as_f32(e.bias, e.bias_dtype, col0 + g * 8, bv);
+              const int src = u * (CHUNK / 8) + g;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[g * 8 + i] += bv[i];
-              }
+              for (int i = 0; i < 8; ++i) v[g * 8 + i] += __shfl_sync(0xffffffffu, bq[i], src);
             }
           }
           activate_block(v, e.act);
