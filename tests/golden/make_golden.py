@@ -2,7 +2,7 @@
 
 Run where the reference is mounted (it is not on the GPU box):
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path of the reference checkout>
 
 Two fixtures:
 
@@ -117,7 +117,9 @@ def golden_llama(ref: Path) -> None:
 
 
 if __name__ == "__main__":
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path of the reference checkout>")
+    ref = Path(sys.argv[1])
     golden_lh_run(ref)
     golden_llama(ref)
     print("wrote", sorted(p.name for p in HERE.iterdir()))
