@@ -43,8 +43,16 @@ struct RowParams {
 // A group of TPR threads per row (one warp, or 4 / 8 warps of a 256-thread block); thread t
 // of the group owns VPL vectors of 8 consecutive elements, vector i covering columns
 // [(i*TPR + t)*8, +8), so a row of up to TPR*VPL*8 elements lives in registers once.
-template <int VPL, int TPR>
-__global__ void __launch_bounds__(256) row_group_kernel(const RowParams p) {
+// SD fixes the element types at compile time (0: read from the parameters; 1: bf16 rows in
+// and out with bf16 scale / shift, the Llama RMSNorm; 2: f32 rows in, bf16 out, f32 scale /
+// shift, the nanoGPT LayerNorm). With run-time types every load, store and rounding carries
+// its type switch, and the kernel is bound by instruction issue and fetch instead of HBM.
+template <int VPL, int TPR, int SD = 0>
+__global__ void __launch_bounds__(256, 4) row_group_kernel(const RowParams p) {
+  const int x_dtype = SD == 1 ? LH_BF16 : SD == 2 ? LH_F32 : p.x_dtype;
+  const int out_dtype = SD != 0 ? LH_BF16 : p.out_dtype;
+  const int gamma_dtype = SD == 1 ? LH_BF16 : SD == 2 ? LH_F32 : p.gamma_dtype;
+  const int beta_dtype = SD == 1 ? LH_BF16 : SD == 2 ? LH_F32 : p.beta_dtype;
   constexpr int GROUPS = 256 / TPR;
   constexpr int WARPS_PER_GROUP = TPR / 32;
   __shared__ float red[2][8];
@@ -75,7 +83,7 @@ __global__ void __launch_bounds__(256) row_group_kernel(const RowParams p) {
   for (int i = 0; i < VPL; ++i) {
     const int c = (i * TPR + t) * 8;
     if (c < p.n) {
-      load8_as_f32(p.x, p.x_dtype, xoff + c, v[i]);
+      load8_as_f32(p.x, x_dtype, xoff + c, v[i]);
     } else {
 #pragma unroll
       for (int k = 0; k < 8; ++k) v[i][k] = (p.mode == 2) ? -INFINITY : 0.f;
@@ -133,14 +141,14 @@ __global__ void __launch_bounds__(256) row_group_kernel(const RowParams p) {
       const int c = (i * TPR + t) * 8;
       if (c < p.n) {
         float g[8], bt[8];
-        if (p.gamma) load8_as_f32(p.gamma, p.gamma_dtype, c, g);
-        if (p.beta) load8_as_f32(p.beta, p.beta_dtype, c, bt);
+        if (p.gamma) load8_as_f32(p.gamma, gamma_dtype, c, g);
+        if (p.beta) load8_as_f32(p.beta, beta_dtype, c, bt);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           float y = (v[i][k] - mean) * rstd;
           // RMSNorm casts the normalised value to the activation type before the weight
           // multiply (examples/llama/ref_model.py:44-47 of the reference)
-          if (p.mode == 1 && p.gamma) y = round_through(y, p.out_dtype);
+          if (p.mode == 1 && p.gamma) y = round_through(y, out_dtype);
           if (p.gamma) y *= g[k];
           if (p.beta) y += bt[k];
           v[i][k] = y;
@@ -153,18 +161,28 @@ __global__ void __launch_bounds__(256) row_group_kernel(const RowParams p) {
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const int c = (i * TPR + t) * 8;
-    if (c < p.n) store8_from_f32(p.out, p.out_dtype, ooff + c, v[i]);
+    if (c < p.n) store8_from_f32(p.out, out_dtype, ooff + c, v[i]);
   }
+}
+
+template <int TPR, int SD>
+void launch_row_group_sd(const RowParams& p, cudaStream_t stream) {
+  const int vpl = (p.n / 8 + TPR - 1) / TPR;
+  const unsigned blocks = static_cast<unsigned>((p.rows + (256 / TPR) - 1) / (256 / TPR));
+  if (vpl <= 1) row_group_kernel<1, TPR, SD><<<blocks, 256, 0, stream>>>(p);
+  else if (vpl <= 2) row_group_kernel<2, TPR, SD><<<blocks, 256, 0, stream>>>(p);
+  else if (vpl <= 3) row_group_kernel<3, TPR, SD><<<blocks, 256, 0, stream>>>(p);
+  else row_group_kernel<4, TPR, SD><<<blocks, 256, 0, stream>>>(p);
 }
 
 template <int TPR>
 void launch_row_group(const RowParams& p, cudaStream_t stream) {
-  const int vpl = (p.n / 8 + TPR - 1) / TPR;
-  const unsigned blocks = static_cast<unsigned>((p.rows + (256 / TPR) - 1) / (256 / TPR));
-  if (vpl <= 1) row_group_kernel<1, TPR><<<blocks, 256, 0, stream>>>(p);
-  else if (vpl <= 2) row_group_kernel<2, TPR><<<blocks, 256, 0, stream>>>(p);
-  else if (vpl <= 3) row_group_kernel<3, TPR><<<blocks, 256, 0, stream>>>(p);
-  else row_group_kernel<4, TPR><<<blocks, 256, 0, stream>>>(p);
+  // the two type combinations of the decoder workloads get kernels with the types compiled in
+  const bool gb_bf16 = (!p.gamma || p.gamma_dtype == LH_BF16) && (!p.beta || p.beta_dtype == LH_BF16);
+  const bool gb_f32 = (!p.gamma || p.gamma_dtype == LH_F32) && (!p.beta || p.beta_dtype == LH_F32);
+  if (p.mode != 2 && p.x_dtype == LH_BF16 && p.out_dtype == LH_BF16 && gb_bf16) launch_row_group_sd<TPR, 1>(p, stream);
+  else if (p.mode != 2 && p.x_dtype == LH_F32 && p.out_dtype == LH_BF16 && gb_f32) launch_row_group_sd<TPR, 2>(p, stream);
+  else launch_row_group_sd<TPR, 0>(p, stream);
 }
 
 // Block per row, any length / alignment; three passes over the row.
