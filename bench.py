@@ -324,8 +324,7 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
         "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {
-            "workload": ("Llama-style decoder stack forward: %d layers, d_model %d, %d q / %d kv heads, head_dim %d, SwiGLU FFN %d, RMSNorm, RoPE, seq %d, batch %d" % (cfg.n_layer, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.seq, cfg.batch))
-            if which == "llama" else ("nanoGPT forward: %d layers, d_model %d, %d heads, GELU MLP x4, pre-LayerNorm, causal, seq %d, batch %d, vocab %d" % (cfg.n_layer, cfg.n_embd, cfg.n_head, cfg.seq, cfg.batch * dp, cfg.vocab)),
+            "workload": workload_description(args),
             "parallelism": f"tp{tp}" + (f"xdp{dp}" if dp > 1 else "") + (f", {'fused multimem reduce+norm+gather kernel' if fused else 'NCCL reduce-scatter/all-gather'} of {args.microbatches} micro-batches overlapped with compute" if overlapped else ""), "tokens_per_step": total_tokens, "l2": "inputs_exceed_l2 (weights + activations >> 126 MB)",
             "algorithmic_tflop_per_step": round(flops / 1e12, 3),
         },
@@ -343,6 +342,9 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
 
 # ---------------------------------------------------------------------------- single kernels
 L2_FLUSH_BYTES = 256 << 20  # > 126 MB of L2: overwritten between timed runs
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised in
+# profiles/gemm_bf16_tc_kernel_4096x4096x4096.md and profiles/attn_fwd_tc2_kernel_b8_h16_s2048_d128.md
+NCU_TRAFFIC_BYTES = {"gemm_4096": 92.8e6, "attention_full": 250.8e6}
 
 
 def kernel_gemm(ctx, peaks, source, K=4096, steps=20, warmup=5) -> dict:
@@ -369,7 +371,7 @@ def kernel_gemm(ctx, peaks, source, K=4096, steps=20, warmup=5) -> dict:
     return {
         "ms": round(mean_s * 1e3, 5), "best_ms": round(float(times.min()) * 1e3, 5), "tflops": round(achieved, 1), "shape": [M, N, K],
         "roofline": {"bound": "tensor", "kernel": "gemm_bf16_tc_kernel", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{source} cuBLAS bf16, burst (kernel timed alone)", "traffic": None},
+                     "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{source} cuBLAS bf16, burst (kernel timed alone)", "traffic": NCU_TRAFFIC_BYTES["gemm_4096"] if K == 4096 else None},
         "host": (a, b, bias, d),
     }
 
@@ -420,7 +422,7 @@ def kernel_attention(ctx, peaks, source, causal=False, steps=20, warmup=5) -> di
     return {
         "ms": round(mean_s * 1e3, 5), "tflops": round(achieved, 1), "causal": causal, "shape": [B, H, S, Dh],
         "roofline": {"bound": "tensor", "kernel": "attn_fwd_tc2_kernel", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{source} cuBLAS bf16, burst (kernel timed alone)", "traffic": None},
+                     "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{source} cuBLAS bf16, burst (kernel timed alone)", "traffic": None if causal else NCU_TRAFFIC_BYTES["attention_full"]},
         "host": (q, k, v, o),
     }
 
@@ -442,14 +444,14 @@ def run_kernel(args, dist: Dist, which: str) -> dict:
         a, b, bias, d = r.pop("host")
         host_ins, dev_out = [a.pin_memory(), b.pin_memory(), bias.pin_memory()], d
         call = lambda ins: ctx.gemm(dev_out, ins[0], ins[1], bias=ins[2], act=1)
-        label = f"bf16 GEMM + bias + ReLU epilogue, M=N=4096, K={args.k}, A,B ~N(0,0.02), bias ~N(0,1), f32 accumulate, bf16 output"
+        label = workload_description(args)
         metric = "gemm_bias_relu_tflops"
     else:
         r = kernel_attention(ctx, peaks, source, causal=args.causal, steps=args.steps, warmup=args.warmup)
         q, k, v, o = r.pop("host")
         host_ins, dev_out = [q.pin_memory(), k.pin_memory(), v.pin_memory()], o
         call = lambda ins: ctx.attention_fwd(dev_out, ins[0], ins[1], ins[2], 128**-0.5, args.causal)
-        label = f"fused flash-attention forward, bf16, batch 8, heads 16, seq 2048, head_dim 128, {'causal' if args.causal else 'non-causal'}"
+        label = workload_description(args)
         metric = "attention_fwd_tflops"
     launches = (ctx.launch_count - launches0) * args.steps // (args.steps + args.warmup)
     # end to end through host buffers: H2D of every operand, the kernel, D2H of the result
@@ -548,6 +550,23 @@ def cpu_sample(which: str, args) -> dict:
 METRICS = {"llama": "llama_decoder_forward_tokens_per_s", "nanogpt": "nanogpt_decoder_forward_tokens_per_s", "gemm": "gemm_bias_relu_tflops", "attention": "attention_fwd_tflops"}
 
 
+def workload_description(args, n_gpus: int = 1) -> str:
+    """The `config.workload` string of a workload, the same for both arms."""
+    from lighthouse_b200.workloads import decoder as D
+
+    if args.workload == "llama":
+        cfg = D.LlamaConfig(n_layer=args.layers or 8)
+        return "Llama-style decoder stack forward: %d layers, d_model %d, %d q / %d kv heads, head_dim %d, SwiGLU FFN %d, RMSNorm, RoPE, seq %d, batch %d" % (
+            cfg.n_layer, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.seq, cfg.batch)
+    if args.workload == "nanogpt":
+        cfg = D.NanoGptConfig(n_layer=args.layers or 12)
+        return "nanoGPT forward: %d layers, d_model %d, %d heads, GELU MLP x4, pre-LayerNorm, causal, seq %d, batch %d, vocab %d" % (
+            cfg.n_layer, cfg.n_embd, cfg.n_head, cfg.seq, cfg.batch, cfg.vocab)
+    if args.workload == "gemm":
+        return f"bf16 GEMM + bias + ReLU epilogue, M=N=4096, K={args.k}, A,B ~N(0,0.02), bias ~N(0,1), f32 accumulate, bf16 output"
+    return f"fused flash-attention forward, bf16, batch 8, heads 16, seq 2048, head_dim 128, {'causal' if args.causal else 'non-causal'}"
+
+
 def reference_arm(args) -> int:
     """`--impl reference`: the CPU baseline on the host cores, on rank 0 only."""
     if int(os.environ.get("RANK", "0")) != 0:
@@ -563,7 +582,7 @@ def reference_arm(args) -> int:
         "impl": "reference", "metric": METRICS[args.workload], "value": round(value, 6), "unit": s["unit"], "n_gpus": args.gpus, "steps": len(samples),
         "warmup": min(args.warmup, 1), "ms_per_step": round(dt / len(samples) * 1e3, 2), "higher_is_better": True,
         "scaling": "strong" if args.workload in ("llama", "nanogpt") else "weak", "vs_baseline": None, "dtype": "f32 arithmetic on bf16-rounded data", "data": "synthetic",
-        "config": {"workload": args.workload, "note": "the reference's own CPU pipeline (lh-run through the MLIR ExecutionEngine) is unavailable: mlir-python-bindings cannot be installed offline; this arm times the CPU oracle port of the same path"},
+        "config": {"workload": workload_description(args), "note": "the reference's own CPU pipeline (lh-run through the MLIR ExecutionEngine) is unavailable: mlir-python-bindings cannot be installed offline; this arm times the CPU oracle port of the same path"},
         "cpu_baseline": {"value": round(value, 6), "unit": s["unit"], "cores": s["cores"], "kind": s["kind"], "sample": s["sample"]},
         "e2e": {"value": round(value, 6), "unit": s["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
