@@ -255,9 +255,12 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
         dev_out = torch.empty(cfg.tokens, cfg.dim, device="cuda", dtype=torch.bfloat16)
     else:
         w = I.nanogpt_weights(cfg.n_layer, cfg.n_embd, cfg.hidden, cfg.vocab, cfg.block_size, seed=4)
-        weights = [t.cuda() for t in D.flatten_nanogpt_args(D.shard_nanogpt_weights(w, cfg, tp_rank, tp))]
-        overlapped = fused = False
-        plan = D.build_nanogpt_plan(cfg, tp_rank, tp)
+        # nanoGPT has no fused collective kernel (LayerNorm, f32 residual); its overlapped schedule
+        # runs on NCCL reduce-scatter / all-gather and is chosen with --collectives nccl
+        fused = False
+        overlapped = tp > 1 and args.microbatches > 0 and args.collectives == "nccl" and (cfg.batch // args.microbatches) % tp == 0
+        weights = [t.cuda() for t in D.flatten_nanogpt_args(D.shard_nanogpt_weights(w, cfg, tp_rank, tp, full_bias=overlapped))]
+        plan = D.build_nanogpt_plan_overlapped(cfg, tp_rank, tp, args.microbatches, args.reserve_sms) if overlapped else D.build_nanogpt_plan(cfg, tp_rank, tp)
         ids = torch.randint(0, cfg.vocab, (cfg.tokens * dp,), generator=torch.Generator().manual_seed(1)).to(torch.int32)
         host_in = ids[group * cfg.tokens : (group + 1) * cfg.tokens].contiguous().pin_memory()
         dev_in = host_in.cuda()
@@ -287,7 +290,7 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
         # (the residual stream is sharded by rows) and every rank ends up with the whole
         # result, so each copies its own rows in and reads its own rows back: together the
         # ranks move the input and the result exactly once.
-        if overlapped:
+        if overlapped and which == "llama":
             tm = cfg.tokens // args.microbatches
             ts = tm // tp
             my_rows = [slice(mb * tm + tp_rank * ts, mb * tm + (tp_rank + 1) * ts) for mb in range(args.microbatches)]

@@ -104,18 +104,20 @@ def check_tp(cfg, tp: int) -> None:
 
 
 # ------------------------------------------------------------------------- weight layout
-def shard_nanogpt_weights(w: dict, cfg: NanoGptConfig, rank: int = 0, tp: int = 1) -> dict:
+def shard_nanogpt_weights(w: dict, cfg: NanoGptConfig, rank: int = 0, tp: int = 1, full_bias: bool = False) -> dict:
     """Reference-layout weights (``oracle.inputs.nanogpt_weights`` keys) -> this rank's
     arrays: q/k/v column blocks of the rank's heads packed side by side into ``wqkv``;
     ``wp`` / ``w2`` row blocks; ``w1`` / ``lmw`` column blocks with their biases. Biases of
-    contracting layers are kept whole on rank 0 and zeroed elsewhere (they are added once)."""
+    contracting layers are kept whole on rank 0 and zeroed elsewhere (they are added once,
+    before the all-reduce) unless ``full_bias``: the row-sharded schedule adds them after the
+    reduce-scatter, each rank on its own rows."""
     import torch
 
     check_tp(cfg, tp)
     c = cfg.n_embd
     cl, hl, vl = c // tp, cfg.hidden // tp, cfg.vocab // tp
     cs, hs, vs = slice(rank * cl, (rank + 1) * cl), slice(rank * hl, (rank + 1) * hl), slice(rank * vl, (rank + 1) * vl)
-    first = rank == 0
+    first = rank == 0 or full_bias
     layers = []
     for lw in w["layers"]:
         layers.append(
@@ -219,6 +221,94 @@ def build_nanogpt_plan(cfg: NanoGptConfig, rank: int = 0, tp: int = 1, name: str
     tail = base + cfg.n_layer * len(GPT_LAYER_KEYS)
     p.layernorm(ln, x, p.arg(tail), p.arg(tail + 1), cfg.eps)
     p.gemm(p.arg(0), ln, p.arg(tail + 2), bias=p.arg(tail + 3))
+    return p
+
+
+def build_nanogpt_plan_overlapped(cfg: NanoGptConfig, rank: int, tp: int, microbatches: int = 2, reserve_sms: int = 8,
+                                  name: str = "nanogpt_forward") -> Plan:
+    """Same arguments and logits as ``build_nanogpt_plan`` (weights sharded with
+    ``full_bias=True``), with the schedule of ``build_llama_plan_overlapped`` on NCCL calls: the
+    f32 residual stream is sharded by rows, each contraction's bf16 partial sums are
+    reduce-scattered, the rank adds them and the layer's bias to its rows, LayerNorm runs on
+    those rows, and the normalised bf16 rows are all-gathered - on the side stream, under
+    the other micro-batch's GEMMs."""
+    check_tp(cfg, tp)
+    check_overlap(cfg.tokens, cfg.batch, tp, microbatches)
+    m = microbatches
+    if (cfg.batch // m) % tp:
+        raise ValueError(f"{cfg.batch // m} sequences per micro-batch do not split into {tp} row blocks of whole sequences")
+    c, t, hs = cfg.n_embd, cfg.tokens, cfg.n_embd // cfg.n_head
+    cl, hl, vl, heads_l = c // tp, cfg.hidden // tp, cfg.vocab // tp, cfg.n_head // tp
+    args = [ArgSpec((t, vl), cfg.logits_dtype, "logits"), ArgSpec((t,), "i32", "ids"), ArgSpec((cfg.vocab, c), "bf16", "wte"), ArgSpec((cfg.block_size, c), "bf16", "wpe")]
+    per_layer = [
+        ((c,), "f32"), ((c,), "f32"), ((c, 3 * cl), "bf16"), ((cl, c), "bf16"), ((c,), "f32"), ((c,), "f32"), ((c,), "f32"),
+        ((c, hl), "bf16"), ((hl,), "f32"), ((hl, c), "bf16"), ((c,), "f32"),
+    ]
+    for li in range(cfg.n_layer):
+        args += [ArgSpec(s_, d_, f"l{li}.{k}") for (s_, d_), k in zip(per_layer, GPT_LAYER_KEYS)]
+    args += [ArgSpec((c,), "f32", "gf_g"), ArgSpec((c,), "f32", "gf_b"), ArgSpec((c, vl), "bf16", "lmw"), ArgSpec((vl,), "f32", "lmb")]
+    p = Plan(name, args)
+    bm, tm = cfg.batch // m, t // m
+    ts = tm // tp
+    x = [p.temp((ts, c), "f32") for _ in range(m)]         # this rank's rows of the residual stream
+    ln = [p.temp((tm, c), "bf16") for _ in range(m)]       # gathered normalised activations
+    qkv = [p.temp((tm, 3 * cl), "bf16") for _ in range(m)]
+    att = [p.temp((tm, cl), "bf16") for _ in range(m)]
+    hbuf = [p.temp((tm, hl), "bf16") for _ in range(m)]
+    part = [p.temp((tm, c), "bf16") for _ in range(m)]     # partial sums of a contraction
+    rs = [p.temp((ts, c), "bf16") for _ in range(m)]
+    chain = _SideChain(p, m)
+    base = 4
+    layer_args = lambda li: {k: p.arg(base + li * len(GPT_LAYER_KEYS) + i) for i, k in enumerate(GPT_LAYER_KEYS)}
+    tail = base + cfg.n_layer * len(GPT_LAYER_KEYS)
+
+    def heads(view2d: PView, col0: int) -> PView:
+        v = view2d.slice(1, col0, cl)
+        return PView(v.slot, (bm, heads_l, cfg.seq, hs), (cfg.seq * v.strides[0], hs, v.strides[0], 1), v.dtype, v.offset)
+
+    def norm_and_gather(mb: int, gamma: PView, beta: PView) -> None:
+        mine = ln[mb].slice(0, rank * ts, ts)
+        p.layernorm(mine, x[mb], gamma, beta, cfg.eps)
+        p.allgather(ln[mb], mine)
+
+    def reduce_into_residual(mb: int, bias: PView) -> None:
+        p.reducescatter(rs[mb], part[mb])
+        p.elementwise("add", x[mb], x[mb], rs[mb])
+        p.elementwise("add", x[mb], x[mb], bias)
+
+    for mb in range(m):
+        chain.fork()
+        # rows of whole sequences: positions restart with each sequence, as in the full batch
+        p.embedding(x[mb], p.arg(1).slice(0, mb * tm + rank * ts, ts), p.arg(2), p.arg(3), period=cfg.seq)
+        norm_and_gather(mb, layer_args(0)["g1"], layer_args(0)["b1n"])
+        chain.join(mb)
+        if mb == 0:
+            p.reserve_sms(reserve_sms)
+    for li in range(cfg.n_layer):
+        a = layer_args(li)
+        for mb in range(m):
+            p.event_wait(chain.ready[mb])
+            p.gemm(qkv[mb], ln[mb], a["wqkv"])
+            p.attention(heads(att[mb], 0), heads(qkv[mb], 0), heads(qkv[mb], cl), heads(qkv[mb], 2 * cl), 1.0 / math.sqrt(hs), cfg.causal)
+            p.gemm(part[mb], att[mb], a["wp"])
+            chain.fork()
+            reduce_into_residual(mb, a["bp"])
+            norm_and_gather(mb, a["g2"], a["b2n"])
+            chain.join(mb)
+        last = li == cfg.n_layer - 1
+        for mb in range(m):
+            p.event_wait(chain.ready[mb])
+            p.gemm(hbuf[mb], ln[mb], a["w1"], bias=a["bb1"], act=cfg.act)
+            p.gemm(part[mb], hbuf[mb], a["w2"])
+            chain.fork()
+            reduce_into_residual(mb, a["bb2"])
+            nxt = (p.arg(tail), p.arg(tail + 1)) if last else (layer_args(li + 1)["g1"], layer_args(li + 1)["b1n"])
+            norm_and_gather(mb, *nxt)
+            chain.join(mb)
+    p.reserve_sms(0)
+    for mb in range(m):
+        p.event_wait(chain.ready[mb])
+        p.gemm(p.arg(0).slice(0, mb * tm, tm), ln[mb], p.arg(tail + 2), bias=p.arg(tail + 3))
     return p
 
 

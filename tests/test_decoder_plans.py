@@ -19,6 +19,7 @@ from oracle.check import max_rel_err
 from lighthouse_b200.workloads import decoder as D
 
 GPT = D.NanoGptConfig(n_layer=2, n_head=4, n_embd=64, vocab=128, block_size=16, batch=2, seq=16, act="gelu", causal=True)
+GPT4 = D.NanoGptConfig(n_layer=2, n_head=4, n_embd=64, vocab=128, block_size=16, batch=4, seq=16, act="gelu", causal=True)  # 2 micro-batches x 2 ranks x whole sequences
 LLAMA = D.LlamaConfig(n_layer=2, dim=128, n_heads=8, n_kv_heads=2, ffn=256, batch=2, seq=16)
 
 
@@ -35,11 +36,11 @@ def llama_reference(cfg, w, x):
     return out.reshape(cfg.tokens, cfg.dim)
 
 
-def run_gpt_rank(cfg, w, ids, rank, tp, allreduce=None):
-    plan = D.build_nanogpt_plan(cfg, rank, tp)
-    sw = D.shard_nanogpt_weights(w, cfg, rank, tp)
+def run_gpt_rank(cfg, w, ids, rank, tp, allreduce=None, overlapped=False):
+    plan = D.build_nanogpt_plan_overlapped(cfg, rank, tp, microbatches=2) if overlapped else D.build_nanogpt_plan(cfg, rank, tp)
+    sw = D.shard_nanogpt_weights(w, cfg, rank, tp, full_bias=overlapped)
     args = [np.zeros((cfg.tokens, cfg.vocab // tp), np.float32), ids.astype(np.int64)] + [I.to_np(t) for t in D.flatten_nanogpt_args(sw)]
-    return CpuPlanRunner(plan, allreduce).run(args)[0]
+    return CpuPlanRunner(plan, allreduce, rank, tp).run(args)[0]
 
 
 def run_llama_rank(cfg, w, x, rank, tp, allreduce=None, overlapped=False, fused=False):
@@ -119,11 +120,13 @@ def _tp_worker(rank, world, port, q):
 
         w, ids = gpt_inputs(GPT)
         logits = run_gpt_rank(GPT, w, ids, rank, world, allreduce)
+        w4, ids4 = gpt_inputs(GPT4)
+        logits_overlapped = run_gpt_rank(GPT4, w4, ids4, rank, world, allreduce, overlapped=True)
         lw, x = llama_inputs(LLAMA)
         hidden = run_llama_rank(LLAMA, lw, x, rank, world, allreduce)
         hidden_overlapped = run_llama_rank(LLAMA, lw, x, rank, world, allreduce, overlapped=True)
         hidden_fused = run_llama_rank(LLAMA, lw, x, rank, world, allreduce, overlapped=True, fused=True)
-        q.put((rank, logits, hidden, hidden_overlapped, hidden_fused))
+        q.put((rank, logits, hidden, hidden_overlapped, hidden_fused, logits_overlapped))
     finally:
         dist.destroy_process_group()
 
@@ -146,7 +149,10 @@ def test_two_rank_tensor_parallel_matches_single_rank():
     assert max_rel_err(logits, full) < 2e-2
     lw, x = llama_inputs(LLAMA)
     want = llama_reference(LLAMA, lw, x)
-    for _, _, hidden, hidden_overlapped, hidden_fused in results:  # the residual stream is replicated after each all-reduce
+    w4, ids4 = gpt_inputs(GPT4)
+    logits4 = np.concatenate([r[5] for r in results], axis=1)
+    assert max_rel_err(logits4, gpt_reference(GPT4, w4, ids4)) < 2e-2  # row-sharded residual, overlapped collectives
+    for _, _, hidden, hidden_overlapped, hidden_fused, _ in results:  # the residual stream is replicated after each all-reduce
         assert max_rel_err(hidden, want) < 2e-2
         assert max_rel_err(hidden_overlapped, want) < 2e-2  # reduce-scatter / all-gather schedule
         assert max_rel_err(hidden_fused, want) < 2e-2  # one fused reduce + norm + gather per sub-block
@@ -180,3 +186,12 @@ def test_overlapped_schedule_is_the_same_computation_and_is_fully_ordered():
     assert fused.kinds().count("reduce_norm_gather") == n_sub + 2 and "reducescatter" not in fused.kinds()
     assert len(fused.args) == len(plan.args) + 4 and fused.args[-1].name == "xn1"
     assert max_rel_err(run_llama_rank(LLAMA, w, x, 0, 1, overlapped=True, fused=True), plain) < 2e-2
+
+
+def test_nanogpt_overlapped_schedule_single_rank_and_limits():
+    w, ids = gpt_inputs(GPT4)
+    plain = run_gpt_rank(GPT4, w, ids, 0, 1)
+    assert max_rel_err(run_gpt_rank(GPT4, w, ids, 0, 1, overlapped=True), plain) < 2e-2
+    assert max_rel_err(plain, gpt_reference(GPT4, w, ids)) < 2e-2
+    with pytest.raises(ValueError):  # one sequence per micro-batch cannot be cut into two row blocks of whole sequences
+        D.build_nanogpt_plan_overlapped(GPT, 0, 2, microbatches=2)
