@@ -273,6 +273,25 @@ class _Importer:
         if name == "layer_norm":
             x = self._tensor(node.args[0], name)
             return self._layer_norm(p, x, a[1], a[2] if len(a) > 2 else kw.get("weight"), a[3] if len(a) > 3 else kw.get("bias"), a[4] if len(a) > 4 else kw.get("eps", 1e-5))
+        if name == "rms_norm":
+            x = self._tensor(node.args[0], name)
+            shape = tuple(a[1])
+            weight = a[2] if len(a) > 2 else kw.get("weight")
+            eps = a[3] if len(a) > 3 else kw.get("eps")
+            if len(shape) != 1 or int(shape[0]) != x.shape[-1]:
+                raise UnsupportedGraph("rms_norm over more than the last dimension")
+            x2 = self._contiguous(p, x).reshape((math.prod(x.shape[:-1]), x.shape[-1]))
+            out = p.temp(x2.shape, x.dtype)
+            p.rmsnorm(out, x2, weight, float(eps) if eps is not None else float(torch.finfo({n: t for t, n in _DTYPE_NAMES.items()}[x.dtype]).eps))
+            return out.reshape(x.shape)
+        if name == "embedding":
+            ids, table = self._tensor(node.args[0], name), self._tensor(node.args[1], name)
+            if ids.dtype not in ("i32", "i64") or table.rank != 2 or any(v is not None for v in a[2:3]) or kw.get("padding_idx") is not None:
+                raise UnsupportedGraph("embedding with a padding index or non-integer ids")
+            flat = self._contiguous(p, ids).reshape((ids.numel,))
+            out = p.temp((ids.numel, table.shape[1]), table.dtype)
+            p.embedding(out, flat, table, None, 0)
+            return out.reshape(tuple(ids.shape) + (table.shape[1],))
         if name == "softmax":
             x = self._tensor(node.args[0], name)
             dim = a[1] if len(a) > 1 else kw.get("dim", -1)

@@ -114,6 +114,30 @@ def test_two_results_and_f32_graph():
         assert max_rel_err(g, w.numpy()) <= 1e-5
 
 
+def test_embedding_rms_norm_and_split_views():
+    class Tiny(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = nn.Embedding(50, 64)
+            self.norm = nn.RMSNorm(64, eps=1e-5)
+            self.up = nn.Linear(64, 256, bias=False)
+            self.down = nn.Linear(128, 64, bias=False)
+
+        def forward(self, ids):
+            h = self.emb(ids)
+            gate, up = self.up(self.norm(h)).chunk(2, dim=-1)
+            return h + self.down(F.silu(gate) * up)
+
+    torch.manual_seed(4)
+    model = Tiny().to(torch.bfloat16)
+    ids = torch.randint(0, 50, (2, 24))
+    plan, results, inputs, want = capture(model, ids)
+    kinds = plan.kinds()
+    assert "embedding" in kinds and "rmsnorm" in kinds and kinds.count("gemm") == 2
+    (got,) = interpret(plan, results, inputs)
+    assert max_rel_err(got, want.float().numpy()) <= TOL_BF16
+
+
 def test_unsupported_graphs_are_value_errors_and_nothing_runs_on_cpu():
     class Sin(nn.Module):
         def forward(self, x):
