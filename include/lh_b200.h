@@ -80,6 +80,10 @@ typedef enum {
 #define LH_GEMM_ACCUMULATE_C 1u /* add `c` BEFORE bias/activation (accumulate_c of gpu_mlp_payload.py:110-156) */
 #define LH_GEMM_FORCE_SIMT 2u   /* use the CUDA-core kernel even if the tensor-core one applies */
 #define LH_GEMM_SWIGLU 4u       /* B holds [gate | up] column blocks; D = silu(gate) * up (N_out = N / 2) */
+/* Bits 8-15: tile width of the tensor-core kernel divided by 8 (64, 128, 192 or 256 columns;
+ * 0 = let the library choose). The hook for a tile database, as the reference's schedules
+ * take wg_tile from matmul_params.json (lighthouse/schedule/xegpu/xegpu_parameter_selector.py:26-85). */
+#define LH_GEMM_TILE_N(n) (((uint32_t)(n) / 8u) << 8)
 
 /* Elementwise op kinds for lh_b200_elementwise. `b` broadcasts over leading
  * dims when its rank is lower than `a`'s (bias add). */

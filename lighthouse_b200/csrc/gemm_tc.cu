@@ -506,6 +506,8 @@ int launch_bn(lh_ctx* ctx, const GemmProblem& p, const EpiParams& epi, int bn) {
 
 int pick_bn(const lh_ctx* ctx, const GemmProblem& p) {
   if (p.flags & LH_GEMM_SWIGLU) return 256;
+  const int hint = static_cast<int>((p.flags >> 8) & 0xffu) * 8;  // the caller's tile database
+  if (hint == 64 || hint == 128 || hint == 192 || hint == 256) return hint;
   const char* env = getenv("LH_B200_GEMM_BN");  // tuning override, read per call
   if (env) {
     const int v = atoi(env);

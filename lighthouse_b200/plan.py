@@ -316,7 +316,7 @@ class Plan:
                     o.operands[j] = v.to_native()
             at = op.attrs
             if op.kind == "gemm":
-                o.i0, o.i1 = ACT_CODES[at.get("act", "none")], int(at.get("flags", 0))
+                o.i0, o.i1 = ACT_CODES[at.get("act", "none")], int(at.get("flags", 0)) | ((int(at.get("tile_n", 0)) // 8) << 8)
             elif op.kind == "attention":
                 o.f0, o.i0 = at["scale"], int(at.get("causal", False))
             elif op.kind in ("layernorm", "rmsnorm", "reduce_norm_gather"):
