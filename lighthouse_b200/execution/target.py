@@ -1,79 +1,85 @@
-"""Target description (the role of lighthouse/execution/target.py:13-132 in the reference).
+"""Which machine a pipeline is being chosen for.
 
-The reference derives ``arch`` from ``platform.machine()`` and ``features`` from ``lscpu``;
-this backend has one target: ``arch="cuda"`` with the compute capability as a feature
-(``sm_100a`` on B200). ``TargetInfo.override`` is kept so tests can fake a target the same
-way the reference's tests do (test/execution/target_info_host_override.py:10-40).
+``TargetInfo`` plays the part of lighthouse/execution/target.py:13-132 in the reference: an
+architecture name plus a feature list that ``find_pipeline_file`` matches descriptor
+directories against. The reference reads ``platform.machine()`` and ``lscpu``; this backend
+knows one architecture, ``cuda``, whose features are compute-capability names (``sm_100a`` and
+``sm_100`` on a B200). Tests fake a target with ``TargetInfo.override(...)`` the way the
+reference's do (test/execution/target_info_host_override.py:10-40).
 """
 
 from __future__ import annotations
 
 from contextlib import contextmanager
 
+_BUILD_TARGET = "sm_100a"
+
+
+def _visible_gpu_features() -> list[str]:
+    """Capability names of device 0 if one is visible, else what the library is built for."""
+    try:
+        import torch
+
+        if torch.cuda.is_available():
+            major, minor = torch.cuda.get_device_capability(0)
+            base = f"sm_{major}{minor}"
+            return [base + "a", base] if major >= 9 else [base]
+    except Exception:  # no torch, no driver: describe the build target
+        pass
+    return [_BUILD_TARGET]
+
 
 class TargetInfo:
-    _cached_host: "TargetInfo | None" = None
-    _override_features_stack: list = []
-    _override_arch_stack: list = []
+    """``arch`` and ``features``; ``filter`` keeps only the listed features."""
+
+    _host: "TargetInfo | None" = None
+    _overrides: list[dict] = []  # innermost ``override(...)`` last
 
     def __init__(self, arch: str | None = None, features: list[str] | None = None, filter: list[str] | None = None):
-        if arch is None and self._override_arch_stack:
-            arch = self._override_arch_stack[-1]
-        if features is None and self._override_features_stack:
-            override = self._override_features_stack[-1]
-            if override is not None:
-                features = list(override)
-        self.arch = arch if arch is not None else "cuda"
-        self.features = features if features is not None else self._get_feature_list()
+        faked = self._overrides[-1] if self._overrides else {}
+        if arch is None:
+            arch = faked.get("arch") or "cuda"
+        if features is None:
+            features = list(faked["features"]) if faked.get("features") is not None else _visible_gpu_features()
+        self.arch, self.features = arch, features
         if filter is not None:
             self.features = self.has_features(filter)
 
+    # -- constructors ------------------------------------------------------------------
     @classmethod
     def host(cls) -> "TargetInfo":
-        if cls._override_features_stack or cls._override_arch_stack:
+        """The machine we are on (cached), or the faked one inside ``override``."""
+        if cls._overrides:
             return cls()
-        if cls._cached_host is None:
-            cls._cached_host = cls()
-        return cls._cached_host
+        if cls._host is None:
+            cls._host = cls()
+        return cls._host
 
     @classmethod
     def cuda(cls) -> "TargetInfo":
-        """The one target this backend executes on."""
-        return cls(arch="cuda", features=["sm_100a"])
+        """The target this backend's kernels are compiled for."""
+        return cls(arch="cuda", features=[_BUILD_TARGET])
 
     @classmethod
     def reset_host_cache(cls) -> None:
-        cls._cached_host = None
+        cls._host = None
 
     @classmethod
     @contextmanager
     def override(cls, *, features: list[str] | None = None, arch: str | None = None):
-        cls._override_features_stack.append(None if features is None else list(features))
-        cls._override_arch_stack.append(arch)
+        cls._overrides.append({"arch": arch, "features": None if features is None else list(features)})
         cls.reset_host_cache()
         try:
             yield
         finally:
-            cls._override_features_stack.pop()
-            cls._override_arch_stack.pop()
+            cls._overrides.pop()
             cls.reset_host_cache()
 
-    def _get_feature_list(self) -> list[str]:
-        """``sm_<major><minor>[a]`` of device 0 when a GPU is visible, else the build target."""
-        try:
-            import torch
-
-            if torch.cuda.is_available():
-                major, minor = torch.cuda.get_device_capability(0)
-                name = f"sm_{major}{minor}"
-                return [name + "a", name] if major >= 9 else [name]
-        except Exception:
-            pass
-        return ["sm_100a"]
-
+    # -- queries -------------------------------------------------------------------------
     def has_features(self, filter: list[str]) -> list[str]:
         return [f for f in self.features if f in filter]
 
     def is_supported(self, hw_extension: str) -> bool:
-        hw_extension = hw_extension.lower()
-        return any(f.startswith(hw_extension) for f in self.features)
+        """True if some feature starts with the name (``sm_100`` matches ``sm_100a``)."""
+        wanted = hw_extension.lower()
+        return any(f.startswith(wanted) for f in self.features)

@@ -20,26 +20,27 @@ from datetime import datetime
 import numpy as np
 
 
+# (flag, argparse keywords): the reference CLI's flags, described in this backend's terms
+_ON_OFF = argparse.BooleanOptionalAction
+_FLAGS = [
+    ("payload_module", dict(type=str, help="MLIR text of the payload (a file path).")),
+    ("--entry-point", dict(type=str, required=True, help="Function of the payload to run.")),
+    ("--input-shape", dict(required=True, help="One DIMSxTYPExINIT field per argument, comma separated: 16x64xf32xrnd,64x32xf32x1 (INIT: 0, 1, rnd, id).")),
+    ("--seed", dict(type=int, default=0, help="Seed of numpy's generator for 'rnd' arguments; 0 takes the clock.")),
+    ("--stage", dict(action="append", required=True, help="A pass name, a pipeline YAML or a backend descriptor; may be given several times, applied in order.")),
+    ("-O", dict(type=int, default=3, help="Kept for command-line compatibility; the kernels are not re-optimised.")),
+    ("--benchmark", dict(action=_ON_OFF, help="Time the entry point instead of running it once.")),
+    ("--print-optimized-module", dict(action=_ON_OFF, help="Print the plan each function was recognised as.")),
+    ("--print-tensor", dict(type=int, default=0, help="Print argument N (1-based) after the run; 0 prints nothing.")),
+    ("--print-mlir-after-all", dict(action=_ON_OFF, help="Print the module after every stage.")),
+]
+
+
 def build_parser() -> argparse.ArgumentParser:
-    p = argparse.ArgumentParser(
-        prog="lh-run",
-        description="Lighthouse runner on B200: optionally applies pipeline stages to an input MLIR payload module and executes it on the GPU.",
-    )
-    p.add_argument("payload_module", type=str, help="Path to the payload MLIR module.")
-    p.add_argument("--entry-point", type=str, required=True, help="Name of the entrypoint function in the payload MLIR module.")
-    p.add_argument(
-        "--input-shape",
-        required=True,
-        help="Shape of the input tensors in format: DIMS(MxNx...)xTYPE(f16/f32/f64/bf16/i8)xINIT(0/1/rnd/id). For multiple inputs, separate by comma.",
-    )
-    p.add_argument("--seed", type=int, default=0, help="Random seed for initializing input tensors.")
-    p.add_argument("--stage", action="append", required=True, help="Pipeline stages to apply to the input module.")
-    p.add_argument("-O", type=int, default=3, help="Optimization level (accepted for compatibility).")
-    p.add_argument("--benchmark", action=argparse.BooleanOptionalAction, help="Whether to run the benchmark. Default is False.")
-    p.add_argument("--print-optimized-module", action=argparse.BooleanOptionalAction, help="Whether to print the recognised module (its plans). Default is False.")
-    p.add_argument("--print-tensor", type=int, default=0, help="Print the Nth tensor. Default is 0 (no print).")
-    p.add_argument("--print-mlir-after-all", action=argparse.BooleanOptionalAction, help="Whether to print the module after every stage. Default is False.")
-    return p
+    parser = argparse.ArgumentParser(prog="lh-run", description="Runs an MLIR payload module on a B200 through the CUDA dispatch pipeline.")
+    for flag, keywords in _FLAGS:
+        parser.add_argument(flag, **keywords)
+    return parser
 
 
 def main(argv=None) -> int:

@@ -36,27 +36,26 @@ class PipelineDriver:
         self.stages.append(lhs.BACKENDS[stage.basename](**stage.opts))
 
     def add_stage(self, stage) -> None:
+        """A ready stage, anything with ``apply(module)``, or a descriptor - which may name a
+        backend, a transform file, a pipeline YAML (expanded into its stages) or a pass."""
         if isinstance(stage, lhs.Stage):
             self.stages.append(stage)
-            return
-        if callable(getattr(stage, "apply", None)) and not isinstance(stage, Descriptor):
+        elif not isinstance(stage, Descriptor):
+            if not callable(getattr(stage, "apply", None)):
+                raise ValueError(f"Unsupported stage type: {type(stage)}")
             self.stages.append(lhs.TransformStage(stage, self.context))
-            return
-        if not isinstance(stage, Descriptor):
-            raise ValueError(f"Unsupported stage type: {type(stage)}")
-        if stage.is_backend():
+        elif stage.is_backend():
             self.add_backend(stage)
-            return
-        filename = stage.basename
-        if os.path.exists(filename):
-            if filename.endswith(".mlir") or filename.endswith(".py"):
+        elif not os.path.exists(stage.basename):
+            self.add_pass(stage)
+        else:
+            extension = os.path.splitext(stage.basename)[1]
+            if extension in (".mlir", ".py"):
                 self.add_transform(stage)
-            elif filename.endswith(".yaml"):
+            elif extension == ".yaml":
                 self.add_stages(PipelineDescriptor(stage).get_stages())
             else:
-                raise ValueError(f"Unknown file type '{os.path.splitext(filename)[1]}' for stage '{stage}'.")
-        else:
-            self.add_pass(stage)
+                raise ValueError(f"Unknown file type '{extension}' for stage '{stage}'.")
 
     def add_stages(self, stages: list) -> None:
         for s in stages:
