@@ -107,3 +107,18 @@ def test_every_tile_width_hint_gives_the_same_product(ctx):
         s.run([d, ad, bd], sync=True)
         s.close()
         assert max_rel_err(d.float().cpu().numpy(), want) <= TOL_BF16, tile_n
+
+
+def test_selector_covers_a_decoder_plan():
+    from lighthouse_b200.workloads import decoder as D
+
+    cfg = D.LlamaConfig(n_layer=2)
+    plan = D.build_llama_plan(cfg)
+    sel = CudaTileSelector()
+    params = sel.select(plan)
+    gemms = [op for op in plan.ops if op.kind == "gemm"]
+    assert len(params) == len(gemms) == 6  # per layer: output projection, gate/up (SwiGLU), down (the q/k/v projection is a gemm_rope)
+    assert {tuple(p["shape"]) for p in params} == {(16384, 4096, 4096), (16384, 28672, 4096), (16384, 4096, 14336)}
+    sel.apply(plan, params)
+    hinted = [op for op in gemms if "tile_n" in op.attrs]
+    assert len(hinted) == 4 and all(op.attrs["tile_n"] == 256 for op in hinted)  # SwiGLU GEMMs keep their fixed width

@@ -187,3 +187,36 @@ def test_torch_compile_on_the_cuda_backend_matches_eager(ctx):
         times = jit.benchmark(*seen["inputs"], nruns=3, nwarmup=1)  # parameters and inputs in graph order
         assert times.shape == (3,) and float(times.min()) > 0
     ctx.use_own_stream()  # the compiled functions had pointed the shared context at torch's stream
+
+
+def test_view_algebra_agrees_with_torch_indexing():
+    """Indexing, transposes and reshapes of the importer are stride arithmetic on ``PView``;
+    the same operations on a torch tensor must select the same elements."""
+    from hypothesis import given, settings, strategies as st
+
+    from lighthouse_b200.ingress.torch.compile import _Importer
+    from lighthouse_b200.plan import PView
+
+    base = torch.arange(4 * 6 * 8).reshape(4, 6, 8)
+    view = PView(0, (4, 6, 8), (48, 8, 1), "i64")
+
+    def gather(v: PView) -> torch.Tensor:
+        return torch.as_strided(base.reshape(-1), v.shape, v.strides, v.offset)
+
+    index = st.one_of(st.integers(-4, 3), st.builds(slice, st.one_of(st.none(), st.integers(0, 3)), st.one_of(st.none(), st.integers(1, 6)), st.one_of(st.none(), st.integers(1, 3))))
+
+    @settings(max_examples=150, deadline=None)
+    @given(i0=index, i1=index, perm=st.permutations([0, 1, 2]))
+    def check(i0, i1, perm):
+        want = base[i0, i1]
+        got = _Importer._index(view, (i0, i1))
+        assert got.shape == tuple(want.shape) and torch.equal(gather(got), want)
+        assert torch.equal(gather(view.permute(perm)), base.permute(perm))
+        if want.dim() == 3 and want.shape[0] * want.shape[1] > 0:
+            try:
+                merged = got.reshape((want.shape[0] * want.shape[1], want.shape[2]))
+            except ValueError:
+                return  # needs a copy: the importer then materialises first
+            assert torch.equal(gather(merged), want.reshape(-1, want.shape[2]))
+
+    check()
