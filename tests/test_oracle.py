@@ -1,5 +1,6 @@
 """Pins the CPU oracle: against the reference's golden vectors, against fixtures generated
-by running the reference's own torch model, and against torch where only a definition exists."""
+by running the reference's own torch model and its own numpy check functions, and against
+torch where only a definition exists (GELU)."""
 
 import json
 import os
@@ -24,6 +25,11 @@ def lh_run_golden():
 @pytest.fixture(scope="module")
 def llama_golden():
     return np.load(os.path.join(GOLDEN, "llama_ref.npz"))
+
+
+@pytest.fixture(scope="module")
+def numpy_checks():
+    return np.load(os.path.join(GOLDEN, "numpy_checks.npz"))
 
 
 def test_lh_run_known_answer(lh_run_golden):
@@ -100,36 +106,93 @@ def test_gemm_epilogue_order_and_rounding():
     assert np.allclose(R.gemm_epilogue(A.T, B.T, transpose_a=True, transpose_b=True), A @ B)
 
 
-def test_nanogpt_block_equals_reference_formula():
-    """nanogpt_block with f16 / ReLU / non-causal / batch 1 must reduce to the reference's own
-    numpy formula (restated inline here from examples/xegpu/nanoGPT.py:84-127)."""
-    rng = np.random.RandomState(5)
-    T, C, H, hid = 16, 32, 4, 64
-    f16 = lambda a: a.astype(np.float16).astype(np.float32)
-    w = dict(
-        g1=np.ones(C, np.float32), b1n=np.zeros(C, np.float32), g2=np.ones(C, np.float32), b2n=np.zeros(C, np.float32),
-        wq=f16(rng.randn(C, C) * 0.1), wk=f16(rng.randn(C, C) * 0.1), wv=f16(rng.randn(C, C) * 0.1), wp=f16(rng.randn(C, C) * 0.1),
-        bp=rng.randn(C).astype(np.float32), w1=f16(rng.randn(C, hid) * 0.1), bb1=rng.randn(hid).astype(np.float32),
-        w2=f16(rng.randn(hid, C) * 0.1), bb2=rng.randn(C).astype(np.float32),
-    )
-    x = (rng.randn(T, C) * 0.5).astype(np.float32)
+# ------------------------------------------------------------------------------------------
+# Fixtures produced by executing the reference's own numpy check functions
+# (tests/golden/make_golden.py::golden_numpy_checks). 16-bit cases: the oracle and the
+# reference evaluate the same formula with differently ordered f32 operations, so a value that
+# sits on a rounding boundary of the 16-bit type may round the other way; the bound is one
+# f16 ulp at the output's scale, everything else agrees to f32 rounding.
+F16_ULP = 2.0**-10
 
-    def ln(z, g, b):
-        mu, var = z.mean(-1, keepdims=True), z.var(-1, keepdims=True)
-        return (z - mu) / np.sqrt(var + 1e-5) * g + b
 
-    ln1 = f16(ln(x, w["g1"], w["b1n"]))
-    q, k, v = f16(ln1 @ w["wq"]), f16(ln1 @ w["wk"]), f16(ln1 @ w["wv"])
-    hs = C // H
-    attn = np.zeros((T, C), np.float32)
-    for h in range(H):
-        sl = slice(h * hs, (h + 1) * hs)
-        s = (q[:, sl] @ k[:, sl].T) / (hs**0.5)
-        e = np.exp(s - s.max(-1, keepdims=True))
-        attn[:, sl] = f16(e / e.sum(-1, keepdims=True)) @ v[:, sl]
-    a = x + f16(attn) @ w["wp"] + w["bp"]
-    ln2 = f16(ln(a, w["g2"], w["b2n"]))
-    want = a + f16(np.maximum(ln2 @ w["w1"] + w["bb1"], 0.0)) @ w["w2"] + w["bb2"]
-    got = R.nanogpt_block(x, w, H, act="relu", causal=False, lowp="f16")
-    # the oracle rounds the attention output to the 16-bit type once more (the kernel's O type)
-    assert max_rel_err(got, want) < 2e-3
+def test_nanogpt_helpers_match_reference_functions(numpy_checks):
+    g = numpy_checks
+    assert_close(R.layernorm(g["gpt_x"], g["gpt_l0_g1"], g["gpt_l0_b1n"], 1e-5), g["gpt_ln"], "f32", "_ln")
+    assert np.array_equal(R.round_to(g["gpt_x"] * 3.3, "f16"), g["gpt_f16"])
+    T, C, H, hid, vocab, L = (int(v) for v in g["gpt_meta"])
+    heads = lambda t: t.reshape(1, T, H, C // H).transpose(0, 2, 1, 3)
+    for causal, key in ((False, "mha_out"), (True, "mha_out_causal")):
+        got = R.attention(heads(g["mha_q"]), heads(g["mha_k"]), heads(g["mha_v"]), causal=causal, io_dtype="f16")
+        # the oracle also rounds O to the 16-bit type (the kernel's output type); _mha returns f32
+        want = g[key].reshape(T, H, C // H).transpose(1, 0, 2)[None]
+        assert max_rel_err(got, R.round_to(want, "f16")) <= F16_ULP, key
+
+
+def _gpt_layers(g, L):
+    keys = ("g1", "b1n", "wq", "wk", "wv", "wp", "bp", "g2", "b2n", "w1", "bb1", "w2", "bb2")
+    return [{k: g[f"gpt_l{i}_{k}"].astype(np.float32) for k in keys} for i in range(L)]
+
+
+def test_nanogpt_block_and_model_match_reference_functions(numpy_checks):
+    g = numpy_checks
+    T, C, H, hid, vocab, L = (int(v) for v in g["gpt_meta"])
+    layers = _gpt_layers(g, L)
+    for causal, key in ((False, "gpt_block"), (True, "gpt_block_causal")):
+        got = R.nanogpt_block(g["gpt_x"], layers[0], H, act="relu", causal=causal, lowp="f16")
+        assert max_rel_err(got, g[key]) <= F16_ULP, key
+        assert np.median(np.abs(got - g[key])) <= 1e-6 * np.abs(g[key]).max()
+    got = R.nanogpt_forward(g["gpt_x"], layers, g["gpt_gf_g"], g["gpt_gf_b"], g["gpt_lmw"].astype(np.float32), g["gpt_lmb"], H, act="relu", causal=False, lowp="f16")
+    assert max_rel_err(got, g["gpt_logits"]) <= 2 * F16_ULP
+    assert np.median(np.abs(got - g["gpt_logits"])) <= 1e-6 * np.abs(g["gpt_logits"]).max()
+
+
+def test_attention_layernorm_softmax_match_reference_checks(numpy_checks):
+    g = numpy_checks
+    f = lambda a: a.astype(np.float32)
+    assert_close(R.attention_unfused_f32(f(g["fa_q"]), f(g["fa_k"]), f(g["fa_v"])), g["fa_out"], "f32", "fused_attention check_correctness")
+    assert_close(R.layernorm(g["ln_x"], g["ln_g"], g["ln_b"], 1e-5), g["ln_out"], "f32", "layer_norm check_correctness")
+    assert_close(R.softmax(g["sm_x"]), g["sm_out"], "f32", "softmax check_correctness")
+
+
+def test_matmul_workload_matches_reference_generator_and_check(numpy_checks):
+    from lighthouse_b200.workloads.matmul import CudaMatMul, matmul_complexity
+
+    g = numpy_checks
+    M, N, K = (int(v) for v in g["mm_meta"])
+    assert tuple(g["mm_complexity"]) == matmul_complexity(4096, 4096, 4096, True, True, False, 2, 2)
+    for i, (bias, relu, acc, trunc, ta, tb, ints) in enumerate(g["mm_variants"].astype(bool)):
+        wl = CudaMatMul(M=M, N=N, K=K, ab_type="f16", c_type="f32", has_bias=bool(bias), has_relu=bool(relu), accumulate_c=bool(acc),
+                        truncate_c=bool(trunc), transpose_a=bool(ta), transpose_b=bool(tb))
+        arrays = wl.get_input_arrays(bool(ints))
+        names = ("C", "A", "B", "bias")[: len(arrays)]
+        for name, arr in zip(names, arrays):  # the seeded inputs themselves
+            assert arr.dtype == g[f"mm{i}_{name}"].dtype and np.array_equal(arr, g[f"mm{i}_{name}"]), (i, name)
+        f = lambda a: a.astype(np.float32)
+        got = R.gemm_epilogue(f(arrays[1]), f(arrays[2]), c=f(arrays[0]) if acc else None, bias=f(arrays[3]) if bias else None,
+                              act="relu" if relu else "none", out_dtype="f16" if trunc else "f32", transpose_a=bool(ta), transpose_b=bool(tb))
+        want = f(g[f"mm{i}_out"])
+        if ints:
+            assert np.array_equal(got, want), i  # small integers: every product and sum is exact
+        else:
+            assert max_rel_err(got, want) <= (F16_ULP if trunc else 1e-6), i
+
+
+def test_mlp_chain_matches_reference_check(numpy_checks):
+    g = numpy_checks
+    f = lambda a: a.astype(np.float32)
+    h = f(g["mlp_x"])
+    for i in range(3):  # ReLU between layers only, every layer's result truncated (examples/xegpu/mlp.py:76-84)
+        h = R.gemm_epilogue(h, f(g[f"mlp_w{i}"]), bias=f(g[f"mlp_b{i}"]), act="relu" if i < 2 else "none", out_dtype="f16")
+    assert max_rel_err(h, f(g["mlp_out"])) <= 2 * F16_ULP
+    assert np.median(np.abs(h - f(g["mlp_out"]))) == 0.0
+
+
+def test_complexity_models_match_reference(numpy_checks):
+    g = numpy_checks
+    # attention: 4 Z H S^2 D flop, Q K V read + O written (examples/xegpu/fused_attention.py:26-43)
+    Z, H, S, D, nb = 8, 16, 2048, 128, 2
+    assert tuple(g["fa_complexity"]) == (4 * Z * H * S * S * D, 3 * Z * H * S * D * nb, Z * H * S * D * nb)
+    # row kernels: one read and one write of the matrix (softmax.py:24-39); layer norm also reads gamma and beta
+    Mr, Nr = 16384, 768
+    assert tuple(g["sm_complexity"])[1:] == (Mr * Nr * 4, Mr * Nr * 4)
+    assert g["ln_complexity"][2] == Mr * Nr * 4 and g["ln_complexity"][1] >= Mr * Nr * 4
