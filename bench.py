@@ -160,9 +160,11 @@ class Dist:
             self.dist.destroy_process_group()
 
 
-def timed_loop(dist: Dist, stream, step, steps: int, warmup: int):
+def timed_loop(dist: Dist, stream, step, steps: int, warmup: int, before_end=None):
     """W untimed steps, then exactly K steps between a barrier + synchronize on both sides,
-    timed with CUDA events on the launching stream; returns the max over ranks in ms."""
+    timed with CUDA events on the launching stream; returns the max over ranks in ms.
+    ``before_end`` makes the launching stream wait for work the steps put on other streams, so
+    that the closing event covers it."""
     import torch
 
     for _ in range(warmup):
@@ -172,6 +174,8 @@ def timed_loop(dist: Dist, stream, step, steps: int, warmup: int):
     e0.record(stream)
     for _ in range(steps):
         step()
+    if before_end is not None:
+        before_end()
     e1.record(stream)
     stream.synchronize()
     dist.barrier()
@@ -196,6 +200,30 @@ def gemm_roofline(plan, op_ms, peaks, which):
         "launches_per_step": sum(1 for op in plan.ops if op.kind in ("gemm", "gemm_rope")),
         "step_time_share": {k: round(v / total, 4) for k, v in sorted(share.items())},
     }
+
+
+def decoder_parity(which: str, cfg, w, host_in, dev_out, tp_rank: int, tp: int) -> dict:
+    """Outside the timed region: the result of the last step, at full depth and full size, on
+    the first 256 positions of two sequences, against the CPU oracle run on those prefixes
+    alone (a causal decoder's prefix depends on nothing after it)."""
+    import torch
+
+    from oracle import prefix as P
+    from oracle.check import parity_report
+
+    torch.cuda.synchronize()
+    seqs, prefix = (0, cfg.batch - 1), 256
+    rows = torch.from_numpy(P.prefix_rows(cfg.seq, seqs, prefix)).to(dev_out.device)
+    got = dev_out[rows].float().cpu().numpy()
+    if which == "llama":
+        ref = P.llama_prefix_reference(w, host_in, cfg, seqs, prefix)
+    else:
+        vl = cfg.vocab // tp
+        ref = P.nanogpt_prefix_reference(w, host_in, cfg, seqs, prefix, vocab_slice=slice(tp_rank * vl, (tp_rank + 1) * vl))
+    rep = parity_report(got, ref, "bf16")
+    rep.update(checked="positions 0..255 of sequences %d and %d of rank 0's result at full depth vs the CPU oracle on those prefixes" % seqs,
+               max_rel_err=float("%.3e" % rep["max_rel_err"]), elementwise_excess=round(rep["elementwise_excess"], 3))
+    return rep
 
 
 # ------------------------------------------------------------------------------- decoders
@@ -265,7 +293,6 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
         host_in = ids[group * cfg.tokens : (group + 1) * cfg.tokens].contiguous().pin_memory()
         dev_in = host_in.cuda()
         dev_out = torch.empty(cfg.tokens, cfg.vocab // tp, device="cuda", dtype=torch.float32)
-    del w
     host_out = torch.empty(dev_out.shape, dtype=dev_out.dtype).pin_memory()
     sess = PlanSession(plan, ctx=ctx)
     dev_args = [dev_out, dev_in] + weights
@@ -297,22 +324,54 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
         else:
             my_rows = None
 
-        def e2e_step():
-            if my_rows:
-                for rows in my_rows:
-                    dev_in[rows].copy_(host_in[rows], non_blocking=True)
-            else:
-                dev_in.copy_(host_in, non_blocking=True)
-            sess.run(dev_args)
-            if my_rows:
-                for rows in my_rows:
-                    host_out[rows].copy_(dev_out[rows], non_blocking=True)
-            elif dist.rank % tp == 0 or which == "nanogpt":
-                host_out.copy_(dev_out, non_blocking=True)
+        # Steps are pipelined the way a serving loop would: two input and two result buffers, the
+        # copy of step i+1's input and the read-back of step i-1's result run on copy streams
+        # under step i's kernels. Every step still moves its own input and its own result.
+        dev_in2, dev_out2 = torch.empty_like(dev_in), torch.empty_like(dev_out)
+        bufs = [(dev_in, dev_out, dev_args), (dev_in2, dev_out2, [dev_out2, dev_in2] + weights)]
+        h2d_stream, d2h_stream = torch.cuda.Stream(), torch.cuda.Stream()
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_done = [torch.cuda.Event() for _ in range(2)]
+        ev_read = [torch.cuda.Event() for _ in range(2)]
+        state = {"i": 0}
+        reads_result = bool(my_rows) or dist.rank % tp == 0 or which == "nanogpt"
 
-        ms_e2e = timed_loop(dist, stream, e2e_step, args.steps, max(1, args.warmup // 2))
+        def e2e_step():
+            b = state["i"] & 1
+            state["i"] += 1
+            d_in, d_out, d_args = bufs[b]
+            h2d_stream.wait_event(ev_done[b])  # the step that last read this input buffer
+            with torch.cuda.stream(h2d_stream):
+                if my_rows:
+                    for rows in my_rows:
+                        d_in[rows].copy_(host_in[rows], non_blocking=True)
+                else:
+                    d_in.copy_(host_in, non_blocking=True)
+                ev_in[b].record(h2d_stream)
+            stream.wait_event(ev_in[b])
+            stream.wait_event(ev_read[b])  # the read-back that last used this result buffer
+            sess.run(d_args)
+            ev_done[b].record(stream)
+            d2h_stream.wait_event(ev_done[b])
+            with torch.cuda.stream(d2h_stream):
+                if my_rows:
+                    for rows in my_rows:
+                        host_out[rows].copy_(d_out[rows], non_blocking=True)
+                elif reads_result:
+                    host_out.copy_(d_out, non_blocking=True)
+                ev_read[b].record(d2h_stream)
+
+        def e2e_loop_end():
+            stream.wait_event(ev_read[0])
+            stream.wait_event(ev_read[1])
+
+        for e in ev_done + ev_read:
+            e.record(stream)
+        ms_e2e = timed_loop(dist, stream, e2e_step, args.steps, max(1, args.warmup // 2), before_end=e2e_loop_end)
         clocks = sampler.stop()
     ctx.sync()  # raises if any kernel gave up on a bounded wait
+    parity = decoder_parity(which, cfg, w, host_in, dev_out, tp_rank, tp) if dist.rank == 0 and not args.no_parity else None
+    del w
     if my_rows:
         h2d = d2h = sum(r.stop - r.start for r in my_rows) * host_in.shape[1] * host_in.element_size()
     else:
@@ -336,6 +395,11 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
         "e2e": {"value": round(total_tokens / (ms_e2e / args.steps * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d_total), "d2h_bytes_per_step": int(d2h_total)},
         "gpu_launches": int(launches), "clocks": clocks,
     }
+    if parity is not None:
+        res["parity"] = parity
+    if which == "llama":
+        per_layer = NCU_TRAFFIC_BYTES.get("llama_gemms_per_layer")
+        res["roofline"]["traffic"] = per_layer * cfg.n_layer if (n == 1 and per_layer) else None
     sess.close()
     if fused:
         symm.close()
@@ -345,9 +409,14 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
 
 # ---------------------------------------------------------------------------- single kernels
 L2_FLUSH_BYTES = 256 << 20  # > 126 MB of L2: overwritten between timed runs
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised in
-# profiles/gemm_bf16_tc_kernel_4096x4096x4096.md and profiles/attn_fwd_tc2_kernel_b8_h16_s2048_d128.md
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, measured once per kernel with
+# `ncu --clock-control none -k regex:<kernel> -c 2..8` on this file's own workloads (the GEMM
+# and attention workloads as they are; the decoder's GEMM launches on a 2-layer stack, summed
+# per layer and multiplied by the layer count, traffic being the same for every layer).
 NCU_TRAFFIC_BYTES = {"gemm_4096": 92.8e6, "attention_full": 250.8e6}
+# The f32 GEMM runs as three tf32 products per f32 product, and the tensor cores run tf32 at
+# half their bf16 rate: its ceiling is a sixth of the measured bf16 peak.
+F32_VIA_TF32X3_FRACTION_OF_BF16 = 1.0 / 6.0
 
 
 def kernel_gemm(ctx, peaks, source, K=4096, steps=20, warmup=5) -> dict:
@@ -379,7 +448,7 @@ def kernel_gemm(ctx, peaks, source, K=4096, steps=20, warmup=5) -> dict:
     }
 
 
-def kernel_gemm_f32(ctx, steps=20, warmup=5) -> dict:
+def kernel_gemm_f32(ctx, peaks, source, steps=20, warmup=5) -> dict:
     """f32 GEMM accumulating into C, M = N = K = 1024, A, B ~ U(-1, 1) (config 1): the lh-run
     matmul. Runs as 3 x TF32 on the tensor cores (two operand-split launches + one tcgen05
     GEMM over 3K); the flop count is the f32 problem's 2MNK."""
@@ -398,8 +467,13 @@ def kernel_gemm_f32(ctx, steps=20, warmup=5) -> dict:
     times = sess.benchmark(dev_args, nruns=steps, nwarmup=warmup, l2_flush_bytes=L2_FLUSH_BYTES)
     sess.close()
     mean_s = float(times.mean())
-    return {"ms": round(mean_s * 1e3, 5), "best_ms": round(float(times.min()) * 1e3, 5), "tflops": round(2.0 * M * N * K / mean_s / 1e12, 2), "shape": [M, N, K],
-            "path": "3xTF32 tcgen05 (split A, split B, GEMM over 3K); f32 result within 1e-5 of the loop nest"}
+    achieved = 2.0 * M * N * K / mean_s / 1e12
+    peak = peaks["bf16_tflops"] * F32_VIA_TF32X3_FRACTION_OF_BF16
+    return {"ms": round(mean_s * 1e3, 5), "best_ms": round(float(times.min()) * 1e3, 5), "tflops": round(achieved, 2), "shape": [M, N, K],
+            "path": "3xTF32 tcgen05; f32 result within 1e-5 of the loop nest",
+            "roofline": {"bound": "tensor", "kernel": "gemm_bf16_tc_kernel<tf32>", "achieved": round(achieved, 2), "peak": round(peak, 1), "unit": "TFLOP/s",
+                         "frac": round(achieved / peak, 4), "peak_source": f"{source} cuBLAS bf16 burst / 6: tf32 at half the bf16 rate, three tf32 products per f32 product", "traffic": None},
+            "reference_published_cpu_gflops": 137.91}
 
 
 def kernel_attention(ctx, peaks, source, causal=False, steps=20, warmup=5) -> dict:
@@ -428,6 +502,140 @@ def kernel_attention(ctx, peaks, source, causal=False, steps=20, warmup=5) -> di
                      "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{source} cuBLAS bf16, burst (kernel timed alone)", "traffic": None if causal else NCU_TRAFFIC_BYTES["attention_full"]},
         "host": (q, k, v, o),
     }
+
+
+def kernel_rowop(ctx, peaks, source, which: str, M: int, N: int, steps=20, warmup=5) -> dict:
+    """Standalone softmax / layer-norm payload (f32, one row kernel): generated as a payload
+    module, recognised, run through the native module; HBM roofline with the reference's byte
+    model, one read and one write of the matrix (examples/xegpu/softmax.py:24-39)."""
+    import torch
+
+    from lighthouse_b200.payload import as_payload_module
+    from lighthouse_b200.payload.generators import generate_gpu_layer_norm_payload, generate_gpu_softmax_payload
+    from lighthouse_b200.workloads.session import PlanSession
+
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(M, N, generator=g).cuda()
+    out = torch.empty_like(x)
+    if which == "softmax":
+        plan = as_payload_module(generate_gpu_softmax_payload("payload", M, N, "f32")).plans["payload"]
+        dev_args = [out, x]
+    else:
+        plan = as_payload_module(generate_gpu_layer_norm_payload("payload", M, N, "f32")).plans["payload"]
+        dev_args = [out, x, torch.randn(N, generator=g).cuda(), torch.randn(N, generator=g).cuda()]
+    kinds = [op.kind for op in plan.ops]
+    sess = PlanSession(plan, ctx=ctx)
+    torch.cuda.synchronize()
+    times = sess.benchmark(dev_args, nruns=steps, nwarmup=warmup, l2_flush_bytes=L2_FLUSH_BYTES)
+    sess.close()
+    mean_s = float(times.mean())
+    nbytes = 2.0 * M * N * 4
+    achieved = nbytes / mean_s / 1e9
+    return {"ms": round(mean_s * 1e3, 5), "gbs": round(achieved, 1), "shape": [M, N], "operators": kinds,
+            "roofline": {"bound": "hbm", "kernel": "row_group_kernel", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": f"{source} copy bandwidth", "traffic": None}}
+
+
+def kernel_nanogpt(ctx, peaks, source, steps=10, warmup=3) -> dict:
+    """nanoGPT forward (config 4: 12 layers, d 768, batch 16, seq 1024, vocab 50304) on one GPU."""
+    import torch
+
+    from lighthouse_b200.workloads import decoder as D
+    from lighthouse_b200.workloads import synthetic as I
+    from lighthouse_b200.workloads.session import PlanSession
+
+    cfg = D.NanoGptConfig()
+    w = I.nanogpt_weights(cfg.n_layer, cfg.n_embd, cfg.hidden, cfg.vocab, cfg.block_size, seed=4)
+    weights = [t.cuda() for t in D.flatten_nanogpt_args(D.shard_nanogpt_weights(w, cfg))]
+    plan = D.build_nanogpt_plan(cfg)
+    ids = torch.randint(0, cfg.vocab, (cfg.tokens,), generator=torch.Generator().manual_seed(1)).to(torch.int32).cuda()
+    logits = torch.empty(cfg.tokens, cfg.vocab, device="cuda", dtype=torch.float32)
+    sess = PlanSession(plan, ctx=ctx)
+    sess.set_profiling(True)
+    dev_args = [logits, ids] + weights
+    torch.cuda.synchronize()  # the context launches on its own stream: operands are complete first
+    for _ in range(warmup):
+        sess.run(dev_args)
+    ctx.sync()
+    stream = torch.cuda.ExternalStream(ctx.stream_handle())
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        sess.run(dev_args)
+    e1.record(stream)
+    ctx.sync()
+    ms = e0.elapsed_time(e1) / steps
+    roof = gemm_roofline(plan, sess.op_times_ms(), peaks, source)
+    sess.close()
+    flops = cfg.flops_per_token() * cfg.tokens
+    return {"ms": round(ms, 4), "tokens_per_s": round(cfg.tokens / (ms * 1e-3), 1), "model_tflops": round(flops / (ms * 1e-3) / 1e12, 1),
+            "algorithmic_tflop_per_step": round(flops / 1e12, 3), "l2": "inputs_exceed_l2 (weights 247 MB, f32 logits 3.3 GB)", "roofline": roof}
+
+
+def e2e_through_runner(ctx, which: str, repeats: int = 3) -> dict:
+    """The reference's own call, timed as a user makes it: ``Runner.execute(name, host numpy
+    buffers, callback)`` with ``GPUMemoryManager`` - device allocation, copies from pageable
+    host arrays, the payload, the read-back in the callback and the frees, all inside the
+    timed region (lighthouse/execution/runner.py:146-224, memory_manager.py:154-168)."""
+    import numpy as np
+
+    from lighthouse_b200.execution import GPUMemoryManager, Runner
+    from lighthouse_b200.payload.generators import generate_gpu_attention_payload
+    from lighthouse_b200.utils.numpy import mlir_to_numpy_dtype
+    from lighthouse_b200.workloads.matmul import CudaMatMul
+
+    bf16 = mlir_to_numpy_dtype("bf16")
+    rng = np.random.RandomState(8)
+    if which == "gemm":
+        M = N = K = 4096
+        wl = CudaMatMul(M=M, N=N, K=K, ab_type="bf16", c_type="f32", has_bias=True, has_relu=True, accumulate_c=False, truncate_c=True)
+        module = wl.payload_module()
+        host = [np.zeros((M, N), bf16), (rng.randn(M, K) * 0.02).astype(bf16), (rng.randn(K, N) * 0.02).astype(bf16), rng.randn(N).astype(bf16)]
+        flops = 2.0 * M * N * K
+    else:
+        Z, H, S, Dh = 8, 16, 2048, 128
+        module = generate_gpu_attention_payload("payload", Z, H, S, Dh, "bf16")
+        host = [np.zeros((Z, H, S, Dh), bf16)] + [rng.randn(Z, H, S, Dh).astype(bf16) for _ in range(3)]
+        flops = 4.0 * Z * H * S * S * Dh
+    out = np.zeros_like(host[0])
+    runner = Runner(module, mem_manager_cls=GPUMemoryManager, context=ctx)
+    cb = Runner.get_gpu_argument_access_callback(out)
+    runner.execute("payload", host, cb)  # warm-up: module creation, kernel attributes
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        runner.execute("payload", host, cb)
+    dt = (time.perf_counter() - t0) / repeats
+    runner.close()
+    assert np.isfinite(out.astype(np.float32)).all()
+    return {"value": round(flops / dt / 1e12, 3), "unit": "TFLOP/s", "ms_per_call": round(dt * 1e3, 3), "clock": "host wall clock around Runner.execute",
+            "h2d_bytes_per_step": int(sum(a.nbytes for a in host)), "d2h_bytes_per_step": int(out.nbytes)}
+
+
+def kernel_lines(dist: Dist, args) -> dict:
+    """Every single-GPU configuration besides the main workload, measured in the same process."""
+    from lighthouse_b200.context import CudaContext
+
+    peaks, source = load_peaks()
+    ctx = CudaContext(dist.local_rank)
+    kernels = {}
+    for K in (1024, 2048, 4096, 8192, 16384):  # config 2 and its K sweep
+        g = kernel_gemm(ctx, peaks, source, K=K)
+        g.pop("host")
+        kernels[f"gemm_bias_relu_4096x4096x{K}"] = g
+    kernels["gemm_f32_1024x1024x1024"] = kernel_gemm_f32(ctx, peaks, source)
+    for causal in (False, True):
+        a = kernel_attention(ctx, peaks, source, causal=causal)
+        a.pop("host")
+        kernels["attention_b8_h16_s2048_d128_" + ("causal" if causal else "full")] = a
+    kernels["softmax_f32_32768x4096"] = kernel_rowop(ctx, peaks, source, "softmax", 32768, 4096)
+    kernels["layer_norm_f32_16384x768"] = kernel_rowop(ctx, peaks, source, "layer_norm", 16384, 768)
+    kernels["layer_norm_f32_131072x768"] = kernel_rowop(ctx, peaks, source, "layer_norm", 131072, 768)
+    if args.workload != "nanogpt":
+        kernels["nanogpt_forward_config4"] = kernel_nanogpt(ctx, peaks, source)
+    kernels["gemm_bias_relu_4096x4096x4096"]["e2e_runner"] = e2e_through_runner(ctx, "gemm")
+    kernels["attention_b8_h16_s2048_d128_full"]["e2e_runner"] = e2e_through_runner(ctx, "attention")
+    ctx.close()
+    return kernels
 
 
 def run_kernel(args, dist: Dist, which: str) -> dict:
@@ -609,6 +817,7 @@ def main() -> int:
     ap.add_argument("--reserve-sms", type=int, default=8, help="SMs the persistent GEMMs leave to the collectives in the overlapped schedule")
     ap.add_argument("--no-kernels", action="store_true", help="skip the GEMM / attention kernel lines of the decoder workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="decoder workloads: skip the full-depth check of the result against the CPU oracle")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
@@ -624,19 +833,7 @@ def main() -> int:
         if args.workload in ("llama", "nanogpt") and not args.no_kernels:
             from lighthouse_b200.context import CudaContext
 
-            peaks, source = load_peaks()
-            ctx = CudaContext(dist.local_rank)
-            kernels = {}
-            g = kernel_gemm(ctx, peaks, source)
-            g.pop("host")
-            kernels["gemm_bias_relu_4096x4096x4096"] = g
-            kernels["gemm_f32_1024x1024x1024"] = kernel_gemm_f32(ctx)
-            for causal in (False, True):
-                a = kernel_attention(ctx, peaks, source, causal=causal)
-                a.pop("host")
-                kernels["attention_b8_h16_s2048_d128_" + ("causal" if causal else "full")] = a
-            ctx.close()
-            res["kernels"] = kernels
+            res["kernels"] = kernel_lines(dist, args)
         if not args.no_cpu_baseline:
             s = cpu_sample(args.workload, args)
             res["cpu_baseline"] = {"value": round(s["value"], 6), "unit": s["unit"], "cores": s["cores"], "kind": s["kind"], "sample": s["sample"]}

@@ -194,8 +194,12 @@ int lh_b200_attention_fwd(lh_ctx_t* ctx, const lh_memref_t* o, const lh_memref_t
  * Sq * Skv <= 1,048,576 and returns LH_ERR_UNSUPPORTED with a message beyond that.
  * Operands are rank-4 (B, H, S, D) views as above; results match lh_b200_attention_fwd's
  * un-fused path. It calls no cudaMalloc / cudaFree and no allocating library routine.
- * The first call on a device looks up the buffer's device address; make that first call
- * outside any stream capture. All calls share the one buffer: two calls whose kernels can
+ * Q, K, V are f32 or bf16, O is f32 or bf16; anything else is rejected before the first
+ * launch. The first call on a device looks up the buffer's device address, and if nothing of
+ * this library has run on that device yet it is also the call on which the CUDA runtime loads
+ * the library's device image, the 4 MiB buffer included: that first call is the warm-up, it
+ * may allocate inside the runtime, and it belongs before any "no allocation" gate and outside
+ * any stream capture. Every later call allocates nothing. All calls share the one buffer: two calls whose kernels can
  * overlap on the GPU (different streams or contexts on one device) race on it.
  */
 int lh_b200_attention_fwd_noalloc(lh_ctx_t* ctx, const lh_memref_t* o, const lh_memref_t* q, const lh_memref_t* k,

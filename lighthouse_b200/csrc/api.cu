@@ -914,14 +914,20 @@ constexpr int NOALLOC_MAX_DEVICES = 64;
 float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
 
 // The array's name is only a host-side handle; the kernels need its address on the device
-// that is current, which the runtime reports per device.
+// they run on, which the runtime reports for the device that is current. The look-up runs
+// once per device with that device made current for its duration (the calling thread's
+// current device is put back before returning).
 int noalloc_scores_ptr(lh_ctx* ctx, float** out) {
   if (ctx->device < 0 || ctx->device >= NOALLOC_MAX_DEVICES)
     return set_error(ctx, LH_ERR_UNSUPPORTED, "attention_fwd_noalloc: device ordinal %d out of range", ctx->device);
   if (!g_noalloc_ptr[ctx->device]) {
-    LH_CUDA_CHECK(ctx, cudaSetDevice(ctx->device));
+    int prev = -1;
+    LH_CUDA_CHECK(ctx, cudaGetDevice(&prev));
+    if (prev != ctx->device) LH_CUDA_CHECK(ctx, cudaSetDevice(ctx->device));
     float* ptr = nullptr;
-    LH_CUDA_CHECK(ctx, cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scores));
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scores);
+    if (prev != ctx->device) (void)cudaSetDevice(prev);
+    LH_CUDA_CHECK(ctx, e);
     g_noalloc_ptr[ctx->device] = ptr;
   }
   *out = g_noalloc_ptr[ctx->device];
@@ -946,15 +952,23 @@ extern "C" int lh_b200_attention_fwd_noalloc(lh_ctx_t* ctx, const lh_memref_t* o
     return set_error(ctx, LH_ERR_UNSUPPORTED, "attention_fwd_noalloc: head_dim must have unit stride");
   if (q->dtype != k->dtype || q->dtype != v->dtype)
     return set_error(ctx, LH_ERR_INVALID, "attention_fwd_noalloc: Q, K, V dtypes differ");
-  const int B = static_cast<int>(q->shape[0]), Hq = static_cast<int>(q->shape[1]), Sq = static_cast<int>(q->shape[2]);
-  const int D = static_cast<int>(q->shape[3]), Hkv = static_cast<int>(k->shape[1]), Skv = static_cast<int>(k->shape[2]);
-  if (B == 0 || Sq == 0) return LH_OK;
-  if (Skv == 0) return set_error(ctx, LH_ERR_INVALID, "attention_fwd_noalloc: empty key sequence");
-  const int64_t score_elems = static_cast<int64_t>(Sq) * Skv;
+  // every check comes before the first launch, so a rejected call leaves nothing half done
+  if (q->dtype != LH_F32 && q->dtype != LH_BF16)
+    return set_error(ctx, LH_ERR_UNSUPPORTED, "attention_fwd_noalloc: Q, K, V must be f32 or bf16 (dtype %d)", q->dtype);
+  if (o->dtype != LH_F32 && o->dtype != LH_BF16)
+    return set_error(ctx, LH_ERR_UNSUPPORTED, "attention_fwd_noalloc: O must be f32 or bf16 (dtype %d)", o->dtype);
+  for (int i = 0; i < 4; ++i)
+    if (q->shape[i] < 0 || k->shape[i] < 0 || q->shape[i] > 0x7fffffffll || k->shape[i] > 0x7fffffffll)
+      return set_error(ctx, LH_ERR_INVALID, "attention_fwd_noalloc: extent out of range");
+  if (q->shape[0] == 0 || q->shape[2] == 0) return LH_OK;
+  if (k->shape[2] == 0) return set_error(ctx, LH_ERR_INVALID, "attention_fwd_noalloc: empty key sequence");
+  const int64_t score_elems = q->shape[2] * k->shape[2];  // both below 2^31: no overflow
   if (score_elems > NOALLOC_MAX_SCORES)
     return set_error(ctx, LH_ERR_UNSUPPORTED,
                      "attention_fwd_noalloc: Sq * Skv = %lld exceeds the built-in score buffer of %lld elements; use lh_b200_attention_fwd",
                      (long long)score_elems, (long long)NOALLOC_MAX_SCORES);
+  const int B = static_cast<int>(q->shape[0]), Hq = static_cast<int>(q->shape[1]), Sq = static_cast<int>(q->shape[2]);
+  const int D = static_cast<int>(q->shape[3]), Hkv = static_cast<int>(k->shape[1]), Skv = static_cast<int>(k->shape[2]);
   float* scores = nullptr;
   int rc = noalloc_scores_ptr(ctx, &scores);
   if (rc) return rc;

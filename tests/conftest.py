@@ -34,6 +34,19 @@ def native_lib():
 
 @pytest.fixture(scope="session")
 def ctx(native_lib):
+    """Launches on torch's current stream: the tests build operands and fill result buffers
+    with torch ops, and stream order is what makes a kernel see them (the context's own
+    stream is non-blocking and would need explicit synchronisation on both sides)."""
+    from lighthouse_b200.context import CudaContext
+
+    c = CudaContext(0, use_torch_stream=True)
+    yield c
+    c.close()
+
+
+@pytest.fixture()
+def own_stream_ctx(native_lib):
+    """A context on its own non-blocking stream; the caller synchronises around its calls."""
     from lighthouse_b200.context import CudaContext
 
     c = CudaContext(0)

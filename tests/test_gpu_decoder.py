@@ -7,8 +7,9 @@ import pytest
 import torch
 
 from oracle import inputs as I
+from oracle import prefix as P
 from oracle import reference_ops as R
-from oracle.check import TOL_BF16, max_rel_err
+from oracle.check import TOL_BF16, max_rel_err, assert_parity
 
 from lighthouse_b200.plan import PlanOp
 from lighthouse_b200.workloads import decoder as D
@@ -55,7 +56,7 @@ def test_nanogpt_forward_matches_oracle(ctx, act, causal):
     wn = I.tree_to_np(w)
     x = R.embed(ids.numpy().reshape(cfg.batch, cfg.seq), wn["wte"], wn["wpe"])
     ref = R.nanogpt_forward(x, wn["layers"], wn["gf_g"], wn["gf_b"], wn["lmw"], wn["lmb"], cfg.n_head, cfg.eps, causal, act, "bf16", cfg.batch)
-    assert max_rel_err(logits.cpu().numpy(), ref) <= TOL_BF16
+    assert_parity(logits.cpu().numpy(), ref, "bf16")
 
 
 def test_llama_forward_matches_oracle(ctx):
@@ -65,7 +66,7 @@ def test_llama_forward_matches_oracle(ctx):
     out = run_llama(ctx, cfg, w, x)
     wn = I.tree_to_np(w)
     ref = R.llama_forward(I.to_np(x).reshape(cfg.batch, cfg.seq, cfg.dim), wn["layers"], wn["norm"], cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True)
-    assert max_rel_err(out.float().cpu().numpy(), ref.reshape(cfg.tokens, cfg.dim)) <= TOL_BF16
+    assert_parity(out.float().cpu().numpy(), ref.reshape(cfg.tokens, cfg.dim), "bf16")
 
 
 def test_tensor_parallel_shards_sum_to_the_full_model_on_one_gpu(ctx):
@@ -94,7 +95,7 @@ def test_tensor_parallel_shards_sum_to_the_full_model_on_one_gpu(ctx):
     lw = wn["layers"][0]
     xr = I.to_np(x).reshape(1, cfg.seq, cfg.dim)
     want = xr + R.llama_attention(R.rmsnorm(xr, lw["attention_norm"], cfg.eps, "bf16"), lw["wq"], lw["wk"], lw["wv"], lw["wo"], cfg.n_heads, cfg.n_kv_heads, cfg.theta, True, "bf16")
-    assert max_rel_err(h_tp, want.reshape(cfg.tokens, cfg.dim)) <= TOL_BF16
+    assert_parity(h_tp, want.reshape(cfg.tokens, cfg.dim), "bf16")
     assert bool(torch.isfinite(full).all())
 
 
@@ -114,7 +115,7 @@ def test_overlapped_schedule_on_one_gpu_matches_the_plain_plan(ctx):
         s.close()
         outs.append(out)
     assert torch.equal(outs[0], outs[1])
-    assert max_rel_err(outs[0].float().cpu().numpy(), plain.cpu().numpy()) <= TOL_BF16
+    assert_parity(outs[0].float().cpu().numpy(), plain.cpu().numpy(), "bf16")
 
 
 def test_fused_schedule_on_one_gpu_matches_the_plain_plan(ctx):
@@ -130,7 +131,7 @@ def test_fused_schedule_on_one_gpu_matches_the_plain_plan(ctx):
     s = PlanSession(plan, ctx=ctx)
     s.run([out, x.cuda()] + cuda_args(D.flatten_llama_args(D.shard_llama_weights(w, cfg))) + extra, sync=True)
     s.close()
-    assert max_rel_err(out.float().cpu().numpy(), plain.cpu().numpy()) <= TOL_BF16
+    assert_parity(out.float().cpu().numpy(), plain.cpu().numpy(), "bf16")
 
 
 @pytest.mark.parametrize("rows,n,with_part", [(96, 4096, True), (7, 256, True), (130, 1024, False)])
@@ -145,7 +146,7 @@ def test_reduce_norm_gather_single_rank_matches_oracle(ctx, rows, n, with_part):
     h_ref = R.round_to(I.to_np(h) + I.to_np(part), "bf16") if with_part else I.to_np(h)
     assert np.array_equal(hd.float().cpu().numpy(), h_ref)  # the residual update is exact in bf16
     want = R.rmsnorm(h_ref, I.to_np(wgt), 1e-5, "bf16")
-    assert max_rel_err(xn.float().cpu().numpy(), want) <= TOL_BF16
+    assert_parity(xn.float().cpu().numpy(), want, "bf16")
     with pytest.raises(ValueError):
         ctx.reduce_norm_gather(xn, None, hd[:, : n - 4], wd, 1e-5)
 
@@ -166,3 +167,31 @@ def test_full_size_configs_run_and_are_deterministic(ctx):
     ids = torch.randint(0, gcfg.vocab, (gcfg.tokens,), generator=torch.Generator().manual_seed(1))
     la, lb = run_nanogpt(ctx, gcfg, gw, ids), run_nanogpt(ctx, gcfg, gw, ids)
     assert torch.equal(la, lb) and bool(torch.isfinite(la).all())
+
+
+def test_config5_full_depth_matches_oracle_on_causal_prefixes(ctx):
+    """The whole Llama configuration (8 layers, d 4096, 32/8 heads, FFN 14336, batch 4, seq 4096)
+    on the GPU; the first 256 positions of two sequences against the oracle run on those
+    prefixes alone (a causal decoder's prefix depends on nothing after it)."""
+    cfg = D.LlamaConfig()
+    w = I.llama_weights(cfg.n_layer, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.ffn, seed=5)
+    x = torch.randn(cfg.tokens, cfg.dim, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    out = run_llama(ctx, cfg, w, x)
+    seqs, prefix = (0, 3), 256
+    rows = torch.from_numpy(P.prefix_rows(cfg.seq, seqs, prefix)).cuda()
+    got = out[rows].float().cpu().numpy()
+    assert_parity(got, P.llama_prefix_reference(w, x, cfg, seqs, prefix), "bf16")
+
+
+def test_config4_full_depth_matches_oracle_on_causal_prefixes(ctx):
+    """The whole nanoGPT configuration (12 layers, d 768, 12 heads, batch 16, seq 1024, vocab
+    50304): f32 logits of the first 256 positions of two sequences against the oracle."""
+    cfg = D.NanoGptConfig()
+    w = I.nanogpt_weights(cfg.n_layer, cfg.n_embd, cfg.hidden, cfg.vocab, cfg.block_size, seed=4)
+    ids = torch.randint(0, cfg.vocab, (cfg.tokens,), generator=torch.Generator().manual_seed(1))
+    logits = run_nanogpt(ctx, cfg, w, ids)
+    seqs, prefix = (0, 11), 256
+    rows = torch.from_numpy(P.prefix_rows(cfg.seq, seqs, prefix)).cuda()
+    got = logits[rows].cpu().numpy()
+    del logits
+    assert_parity(got, P.nanogpt_prefix_reference(w, ids, cfg, seqs, prefix), "bf16")

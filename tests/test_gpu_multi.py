@@ -12,7 +12,7 @@ import torch
 
 from oracle import inputs as I
 from oracle import reference_ops as R
-from oracle.check import TOL_BF16, max_rel_err
+from oracle.check import TOL_BF16, max_rel_err, assert_parity
 
 pytestmark = pytest.mark.gpu
 
@@ -124,8 +124,8 @@ def test_two_ranks_on_two_gpus_match_the_oracle():
     for rank, op_xn, op_h, _, _ in results:
         # the switch returns its f32 sum in the activation type with a rounding of its own:
         # the residual rows agree to bf16 precision, not bit for bit
-        assert max_rel_err(op_h, h[rank * rows : (rank + 1) * rows]) <= TOL_BF16
-        assert max_rel_err(op_xn, want_xn) <= TOL_BF16  # every rank holds every rank's rows
+        assert_parity(op_h, h[rank * rows : (rank + 1) * rows], "bf16")
+        assert_parity(op_xn, want_xn, "bf16")  # every rank holds every rank's rows
     assert np.array_equal(results[0][1], results[1][1])
 
     # decoder: all three schedules against the single-rank oracle, and replicated across ranks
@@ -139,5 +139,5 @@ def test_two_ranks_on_two_gpus_match_the_oracle():
     ref = ref.reshape(cfg.tokens, cfg.dim)
     for name in ("allreduce", "nccl_overlapped", "fused_overlapped"):
         for r in results:
-            assert max_rel_err(r[3][name], ref) <= TOL_BF16, name
+            assert_parity(r[3][name], ref, "bf16")
         assert np.array_equal(results[0][3][name], results[1][3][name]), name

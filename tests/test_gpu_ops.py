@@ -9,7 +9,7 @@ import torch
 from oracle import build as oracle_build
 from oracle import inputs as I
 from oracle import reference_ops as R
-from oracle.check import TOL_BF16, TOL_F32, max_rel_err
+from oracle.check import TOL_BF16, TOL_F32, max_rel_err, assert_parity
 
 from lighthouse_b200 import _native as N
 
@@ -39,7 +39,7 @@ def test_gemm_f32_matches_loop_nest(ctx, shape):
     d = dev(c.copy())
     ctx.gemm(d, dev(a), dev(b), c=d)
     ctx.sync()
-    assert max_rel_err(host(d), ref) <= TOL_F32
+    assert_parity(host(d), ref, "f32")
 
 
 @pytest.mark.parametrize("shape", [(300, 264, 77), (129, 512, 1000), (2048, 128, 9)])
@@ -54,22 +54,22 @@ def test_gemm_f32_tensor_core_split_path(ctx, shape):
     d = dev(c.copy())
     ctx.gemm(d, dev(a), dev(b), c=d)
     ctx.sync()
-    assert max_rel_err(host(d), ref) <= TOL_F32
+    assert_parity(host(d), ref, "f32")
     d2 = dev(c.copy())
     ctx.gemm(d2, dev(np.ascontiguousarray(a.T)).t(), dev(np.ascontiguousarray(b.T)).t(), c=d2)
     ctx.sync()
-    assert max_rel_err(host(d2), ref) <= TOL_F32
+    assert_parity(host(d2), ref, "f32")
     bias, res = np.random.RandomState(3).randn(n).astype(np.float32), np.random.RandomState(4).randn(m, n).astype(np.float32)
     d3 = torch.zeros(m, n, device="cuda")
     ctx.gemm(d3, dev(a), dev(b), bias=dev(bias), residual=dev(res), act=N.ACT_RELU)
     ctx.sync()
     want = np.maximum(oracle_build.matmul_loops(a, b, np.zeros((m, n), np.float32)) + bias, 0) + res
-    assert max_rel_err(host(d3), want) <= TOL_F32
+    assert_parity(host(d3), want, "f32")
     # the CUDA-core kernel on request, same answer
     d4 = dev(c.copy())
     ctx.gemm(d4, dev(a), dev(b), c=d4, flags=N.GEMM_FORCE_SIMT)
     ctx.sync()
-    assert max_rel_err(host(d4), host(d)) <= TOL_F32
+    assert_parity(host(d4), host(d), "f32")
 
 
 def test_gemm_f32_config1_full_size(ctx):
@@ -79,12 +79,12 @@ def test_gemm_f32_config1_full_size(ctx):
     d = dev(c)
     ctx.gemm(d, dev(a), dev(b))
     ctx.sync()
-    assert max_rel_err(host(d), ref) <= TOL_F32
+    assert_parity(host(d), ref, "f32")
     # strided views: A^T given as a transposed view, same answer
     d2 = torch.zeros_like(d)
     ctx.gemm(d2, dev(np.ascontiguousarray(a.T)).t(), dev(b))
     ctx.sync()
-    assert max_rel_err(host(d2), ref) <= TOL_F32
+    assert_parity(host(d2), ref, "f32")
 
 
 def test_gemm_empty_and_degenerate(ctx):
@@ -112,12 +112,12 @@ def test_gemm_bf16_bias_relu(ctx, layout, shape, out):
     d = torch.full((m, n), 7.0, device="cuda", dtype=torch.bfloat16 if out == "bf16" else torch.float32)
     ctx.gemm(d, dev(a), bd, bias=dev(bias), act=N.ACT_RELU)
     ctx.sync()
-    assert max_rel_err(host(d), ref) <= (TOL_BF16 if out == "bf16" else 1e-5)
+    assert_parity(host(d), ref, out)
     # the CUDA-core kernel must agree with the tensor-core kernel
     d2 = torch.empty_like(d)
     ctx.gemm(d2, dev(a), bd, bias=dev(bias), act=N.ACT_RELU, flags=N.GEMM_FORCE_SIMT)
     ctx.sync()
-    assert max_rel_err(host(d2), ref) <= (TOL_BF16 if out == "bf16" else 1e-5)
+    assert_parity(host(d2), ref, out)
 
 
 @pytest.mark.parametrize("act", ["none", "gelu", "gelu_tanh", "silu"])
@@ -134,7 +134,7 @@ def test_gemm_bf16_full_epilogue(ctx, act, out):
     d = dev(res.clone())
     ctx.gemm(d, dev(a), dev(b), c=dev(c), bias=dev(bias), residual=d, act=ACT[act])
     ctx.sync()
-    assert max_rel_err(host(d), ref) <= (TOL_BF16 if out == "bf16" else 2e-5)
+    assert_parity(host(d), ref, out, tol=TOL_BF16 if out == "bf16" else 2e-5)
 
 
 def test_gemm_swiglu_epilogue(ctx):
@@ -148,7 +148,7 @@ def test_gemm_swiglu_epilogue(ctx):
     d = torch.empty(m, f, device="cuda", dtype=torch.bfloat16)
     ctx.gemm(d, dev(x), dev(pack_swiglu(w1, w3)).t(), flags=N.GEMM_SWIGLU)
     ctx.sync()
-    assert max_rel_err(host(d), ref) <= TOL_BF16
+    assert_parity(host(d), ref, "bf16")
 
 
 def test_gemm_config2_full_size_properties(ctx):
@@ -161,7 +161,7 @@ def test_gemm_config2_full_size_properties(ctx):
     ctx.sync()
     rows = [0, 1, 127, 128, 2049, 4095]
     ref = R.gemm_epilogue(I.to_np(a[rows]), I.to_np(b), bias=I.to_np(bias), act="relu", out_dtype="bf16")
-    assert max_rel_err(host(d[rows]), ref) <= TOL_BF16
+    assert_parity(host(d[rows]), ref, "bf16")
     d2 = torch.empty_like(d)
     ctx.gemm(d2, ad, bd, bias=biasd, act=N.ACT_RELU)
     ctx.sync()
@@ -181,7 +181,7 @@ def test_batched_gemm(ctx):
     d = torch.empty(3, 40, 56, device="cuda")
     ctx.gemm(d, dev(a), dev(b))
     ctx.sync()
-    assert max_rel_err(host(d), np.einsum("bmk,bkn->bmn", I.to_np(a), I.to_np(b))) <= 1e-5
+    assert_parity(host(d), np.einsum("bmk,bkn->bmn", I.to_np(a), I.to_np(b)), "f32")
 
 
 # --------------------------------------------------------------------------------- attention
@@ -194,7 +194,7 @@ def test_attention_bf16(ctx, shape, causal):
     o = torch.full_like(q, 5.0).cuda()
     ctx.attention_fwd(o, dev(q), dev(k), dev(v), d**-0.5, causal)
     ctx.sync()
-    assert max_rel_err(host(o), ref) <= TOL_BF16
+    assert_parity(host(o), ref, "bf16")
 
 
 def test_attention_strided_views_and_f32_output(ctx):
@@ -212,7 +212,7 @@ def test_attention_strided_views_and_f32_output(ctx):
     ctx.attention_fwd(heads(out, 0), heads(qkv_d, 0), heads(qkv_d, c), heads(qkv_d, 2 * c), hs**-0.5, True)
     ctx.sync()
     ref = R.attention(I.to_np(heads(qkv, 0)), I.to_np(heads(qkv, c)), I.to_np(heads(qkv, 2 * c)), causal=True, io_dtype="bf16")
-    assert max_rel_err(host(heads(out, 0)), ref) <= TOL_BF16
+    assert_parity(host(heads(out, 0)), ref, "bf16")
 
 
 def test_attention_f32_unfused_path(ctx):
@@ -220,7 +220,7 @@ def test_attention_f32_unfused_path(ctx):
     o = torch.empty(2, 2, 64, 32, device="cuda")
     ctx.attention_fwd(o, dev(q), dev(k), dev(v), 32**-0.5, False)
     ctx.sync()
-    assert max_rel_err(host(o), R.attention_unfused_f32(I.to_np(q), I.to_np(k), I.to_np(v))) <= 1e-5
+    assert_parity(host(o), R.attention_unfused_f32(I.to_np(q), I.to_np(k), I.to_np(v)), "f32")
 
 
 def test_attention_config3_full_size_properties(ctx):
@@ -233,7 +233,7 @@ def test_attention_config3_full_size_properties(ctx):
         ctx.attention_fwd(o, qd, kd, vd, 128**-0.5, causal)
         ctx.sync()
         ref = R.attention(I.to_np(q[3:4, 5:6]), I.to_np(k[3:4, 5:6]), I.to_np(v[3:4, 5:6]), causal=causal, io_dtype="bf16")
-        assert max_rel_err(host(o[3:4, 5:6]), ref) <= TOL_BF16
+        assert_parity(host(o[3:4, 5:6]), ref, "bf16")
         o2 = torch.empty_like(qd)
         ctx.attention_fwd(o2, qd, kd, vd * 2, 128**-0.5, causal)
         ctx.sync()
@@ -251,7 +251,7 @@ def test_layernorm(ctx, rows, n, xdt, odt):
     out = torch.empty(rows, n, device="cuda", dtype=tdt[odt])
     ctx.layernorm(out, dev(x, tdt[xdt]), dev(g), dev(b), 1e-5)
     ctx.sync()
-    assert max_rel_err(host(out), R.round_to(R.layernorm(x, g, b, 1e-5), odt)) <= (TOL_BF16 if odt == "bf16" else TOL_F32)
+    assert_parity(host(out), R.round_to(R.layernorm(x, g, b, 1e-5), odt), odt)
 
 
 @pytest.mark.parametrize("rows,n", [(512, 4096), (7, 128), (3, 1000)])
@@ -262,11 +262,11 @@ def test_rmsnorm(ctx, rows, n):
     out = torch.empty(rows, n, device="cuda", dtype=torch.bfloat16)
     ctx.rmsnorm(out, dev(x, torch.bfloat16), dev(w, torch.bfloat16), 1e-5)
     ctx.sync()
-    assert max_rel_err(host(out), R.rmsnorm(x, w, 1e-5, "bf16")) <= TOL_BF16
+    assert_parity(host(out), R.rmsnorm(x, w, 1e-5, "bf16"), "bf16")
     out32 = torch.empty(rows, n, device="cuda")
     ctx.rmsnorm(out32, dev(x), None, 1e-5)
     ctx.sync()
-    assert max_rel_err(host(out32), R.rmsnorm(x, None, 1e-5, "f32")) <= TOL_F32
+    assert_parity(host(out32), R.rmsnorm(x, None, 1e-5, "f32"), "f32")
 
 
 @pytest.mark.parametrize("rows,n", [(300, 1000), (64, 768), (2, 9000)])
@@ -275,7 +275,7 @@ def test_softmax(ctx, rows, n):
     out = torch.empty(rows, n, device="cuda")
     ctx.softmax(out, dev(x))
     ctx.sync()
-    assert max_rel_err(host(out), R.softmax(x)) <= TOL_F32
+    assert_parity(host(out), R.softmax(x), "f32")
     np.testing.assert_allclose(host(out).sum(-1), 1.0, rtol=1e-5)
 
 
@@ -284,11 +284,11 @@ def test_rope(ctx):
     t = dev(x, torch.bfloat16)
     ctx.rope(t, 10000.0, 0)
     ctx.sync()
-    assert max_rel_err(host(t), R.rope(x, 10000.0, 0, "bf16")) <= TOL_BF16
+    assert_parity(host(t), R.rope(x, 10000.0, 0, "bf16"), "bf16")
     t32 = dev(x)
     ctx.rope(t32, 10000.0, 7)
     ctx.sync()
-    assert max_rel_err(host(t32), R.rope(x, 10000.0, 7, "f32")) <= 1e-4  # angles up to ~300 rad in f32
+    assert_parity(host(t32), R.rope(x, 10000.0, 7, "f32"), "f32", tol=1e-4)  # angles up to ~300 rad in f32
 
 
 def test_elementwise_family_and_embedding(ctx):
@@ -304,7 +304,7 @@ def test_elementwise_family_and_embedding(ctx):
     for kind, ops, kw, ref in cases:
         ctx.elementwise(kind, out, *ops, **kw)
         ctx.sync()
-        assert max_rel_err(host(out), ref) <= 1e-5, kind
+        assert_parity(host(out), ref, "f32")
     # cast + transposing copy through strided views
     o16 = torch.empty(256, 64, device="cuda", dtype=torch.bfloat16)
     ctx.elementwise(N.EW_COPY, o16, ad.t())
@@ -324,6 +324,21 @@ def test_launch_counter_and_status_word(ctx):
     ctx.elementwise(N.EW_FILL, t, scalar=1.0)
     ctx.sync()  # also reads the device status word: no bounded wait ran out
     assert ctx.launch_count == before + 1 and float(t.sum()) == 64.0
+
+
+def test_own_stream_mode_with_explicit_synchronisation(own_stream_ctx):
+    """A context on its own non-blocking stream is ordered with torch by synchronising: torch's
+    stream before the call (operands and the result buffer's fill are complete), the
+    context's after it."""
+    c = own_stream_ctx
+    a, b, bias = I.gemm_bf16_normal(256, 384, 128, seed=17)
+    a, b = a * 25, b * 25
+    ad, bd, biasd = dev(a), dev(b), dev(bias)
+    d = torch.full((256, 384), float("nan"), device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    c.gemm(d, ad, bd, bias=biasd, act=N.ACT_RELU)
+    c.sync()
+    assert_parity(host(d), R.gemm_epilogue(I.to_np(a), I.to_np(b), bias=I.to_np(bias), act="relu", out_dtype="bf16"), "bf16")
 
 
 def test_side_stream_events_and_collectives_of_one_rank(ctx):
@@ -371,7 +386,7 @@ def test_gemm_with_rotary_epilogue(ctx, m, n, k, cols, hd, seq):
     ctx.sync()
     want = R.round_bf16(a @ b)
     want[:, :cols] = R.rope(want[:, :cols].reshape(m // seq, seq, cols // hd, hd), 10000.0, 3, "bf16").reshape(m, cols)
-    assert max_rel_err(host(d), want) <= TOL_BF16
+    assert_parity(host(d), want, "bf16")
     # untouched columns are the plain product
     plain = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
     ctx.gemm(plain, dev(a, torch.bfloat16), dev(b, torch.bfloat16))

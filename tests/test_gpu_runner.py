@@ -12,7 +12,7 @@ import torch
 from conftest import GOLDEN, PAYLOADS
 from oracle import inputs as I
 from oracle import reference_ops as R
-from oracle.check import TOL_BF16, TOL_F32, max_rel_err
+from oracle.check import TOL_BF16, TOL_F32, max_rel_err, assert_parity
 
 from lighthouse_b200.execution import GPUMemoryManager, Runner, TorchCudaMemoryManager
 from lighthouse_b200.payload import generators as G
@@ -73,7 +73,7 @@ def test_runner_gpu_memory_manager_and_callback(ctx):
     runner.execute("payload", [C, A, B, bias], Runner.get_gpu_argument_access_callback(out, arg_index=0))
     f = lambda x: np.asarray(x, dtype=np.float32)
     ref = R.gemm_epilogue(f(A), f(B), bias=f(bias), act="relu", out_dtype="bf16")
-    assert max_rel_err(f(out), ref) <= TOL_BF16
+    assert_parity(f(out), ref, "bf16")
     times = runner.benchmark([C, A, B, bias], nruns=7, nwarmup=2)
     assert times.shape == (7,) and times.dtype == np.float64 and np.all(times > 0) and np.all(times < 1.0)
     flops, reads, writes = wl.get_complexity()
@@ -94,7 +94,7 @@ def test_matmul_example_defaults_accumulate_c(ctx, init_int):
     if init_int:
         assert np.array_equal(out, ref)
     else:
-        assert max_rel_err(out, ref) <= TOL_F32
+        assert_parity(out, ref, "f32")
     runner.close()
 
 
@@ -108,7 +108,7 @@ def test_runner_torch_pass_through(ctx):
     runner.execute("payload", [o, q.cuda(), k.cuda(), v.cuda()], lambda inputs, **kw: seen.update(kw, n=len(inputs)))
     assert seen["n"] == 4 and seen["memory_manager"] is not None and seen["execution_engine"] is ctx
     ref = R.attention(I.to_np(q), I.to_np(k), I.to_np(v), io_dtype="bf16")
-    assert max_rel_err(o.float().cpu().numpy(), ref) <= TOL_BF16
+    assert_parity(o.float().cpu().numpy(), ref, "bf16")
     with pytest.raises(ValueError):
         runner.execute("payload", [o.cpu(), q, k, v])
     runner.close()
@@ -122,24 +122,24 @@ def test_generated_payloads_through_text(ctx):
     out = np.zeros_like(x)
     r = Runner(str(G.generate_gpu_layer_norm_payload("payload", 96, 768, "f32")), context=ctx)
     r.execute("payload", [out, x, g, b])
-    assert max_rel_err(out, R.layernorm(x, g, b)) <= TOL_F32
+    assert_parity(out, R.layernorm(x, g, b), "f32")
     r.close()
     r = Runner(str(G.generate_gpu_softmax_payload("payload", 96, 768, "f32")), context=ctx)
     r.execute("payload", [out, x])
-    assert max_rel_err(out, R.softmax(x)) <= TOL_F32
+    assert_parity(out, R.softmax(x), "f32")
     r.close()
     q, k, v = (rng.randn(2, 2, 48, 32).astype(np.float32) for _ in range(3))
     o = np.zeros_like(q)
     r = Runner(str(G.generate_gpu_attention_payload("payload", 2, 2, 48, 32, "f32")), context=ctx)
     r.execute("payload", [o, q, k, v])
-    assert max_rel_err(o, R.attention_unfused_f32(q, k, v)) <= 1e-5
+    assert_parity(o, R.attention_unfused_f32(q, k, v), "f32")
     r.close()
     wl = CudaMatMul(M=128, N=64, K=256, ab_type="bf16", c_type="f32", accumulate_c=False, transpose_a=True, transpose_b=True, has_relu=True)
     C, A, B = wl.get_input_arrays()
     r = Runner(str(wl.payload_module()), context=ctx)
     r.execute("payload", [C, A, B])
     f = lambda t: np.asarray(t, dtype=np.float32)
-    assert max_rel_err(C, R.gemm_epilogue(f(A), f(B), act="relu", transpose_a=True, transpose_b=True)) <= TOL_F32
+    assert_parity(C, R.gemm_epilogue(f(A), f(B), act="relu", transpose_a=True, transpose_b=True), "f32")
     r.close()
 
 
@@ -162,7 +162,7 @@ def test_fused_and_unfused_pipelines_agree(ctx):
         os.remove(path)
     assert outs[0][0] == 1 and outs[1][0] > 1 and outs[2][0] == 1
     assert np.array_equal(outs[0][1], outs[2][1])
-    assert max_rel_err(outs[1][1], outs[0][1]) <= TOL_BF16
+    assert_parity(outs[1][1], outs[0][1], "bf16")
 
 
 def test_nanogpt_payload_module_end_to_end(ctx):

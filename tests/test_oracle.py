@@ -196,3 +196,29 @@ def test_complexity_models_match_reference(numpy_checks):
     Mr, Nr = 16384, 768
     assert tuple(g["sm_complexity"])[1:] == (Mr * Nr * 4, Mr * Nr * 4)
     assert g["ln_complexity"][2] == Mr * Nr * 4 and g["ln_complexity"][1] >= Mr * Nr * 4
+
+
+def test_causal_prefix_property_of_the_decoder_oracles():
+    """What the full-size GPU parity tests rely on: the first t positions of a causal decoder's
+    output depend on the first t inputs only, so the oracle run on a prefix reproduces those
+    rows of the oracle run on whole sequences."""
+    from lighthouse_b200.workloads import decoder as D
+    from oracle import prefix as P
+
+    cfg = D.LlamaConfig(n_layer=2, dim=64, n_heads=4, n_kv_heads=2, ffn=128, batch=3, seq=24)
+    w = I.llama_weights(cfg.n_layer, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.ffn, seed=5, std=0.1)
+    x = torch.randn(cfg.tokens, cfg.dim, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    wn = I.tree_to_np(w)
+    full = R.llama_forward(I.to_np(x).reshape(cfg.batch, cfg.seq, cfg.dim), wn["layers"], wn["norm"], cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True)
+    rows = P.prefix_rows(cfg.seq, (0, 2), 9)
+    got = P.llama_prefix_reference(w, x, cfg, (0, 2), 9)
+    assert max_rel_err(got, full.reshape(cfg.tokens, cfg.dim)[rows]) <= 1e-6
+
+    g = D.NanoGptConfig(n_layer=2, n_head=4, n_embd=64, vocab=96, block_size=32, batch=3, seq=24)
+    gw = I.nanogpt_weights(g.n_layer, g.n_embd, g.hidden, g.vocab, g.block_size, seed=4, std=0.1)
+    ids = torch.randint(0, g.vocab, (g.tokens,), generator=torch.Generator().manual_seed(1))
+    gn = I.tree_to_np(gw)
+    xe = R.embed(ids.numpy().reshape(g.batch, g.seq), gn["wte"], gn["wpe"])
+    full = R.nanogpt_forward(xe, gn["layers"], gn["gf_g"], gn["gf_b"], gn["lmw"], gn["lmb"], g.n_head, g.eps, True, g.act, "bf16", g.batch)
+    got = P.nanogpt_prefix_reference(gw, ids, g, (1, 2), 7, vocab_slice=slice(48, 96))
+    assert max_rel_err(got, full[P.prefix_rows(g.seq, (1, 2), 7), 48:96]) <= 1e-6

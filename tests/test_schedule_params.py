@@ -91,7 +91,7 @@ def test_every_tile_width_hint_gives_the_same_product(ctx):
     import torch
 
     from oracle import reference_ops as R
-    from oracle.check import TOL_BF16, max_rel_err
+    from oracle.check import TOL_BF16, max_rel_err, assert_parity
     from lighthouse_b200.workloads.session import PlanSession
 
     rng = np.random.RandomState(5)
@@ -106,7 +106,7 @@ def test_every_tile_width_hint_gives_the_same_product(ctx):
         s = PlanSession(plan, ctx=ctx)
         s.run([d, ad, bd], sync=True)
         s.close()
-        assert max_rel_err(d.float().cpu().numpy(), want) <= TOL_BF16, tile_n
+        assert_parity(d.float().cpu().numpy(), want, "bf16")
 
 
 def test_selector_covers_a_decoder_plan():

@@ -13,7 +13,7 @@ import torch.nn.functional as F
 
 from cpu_plan import CpuPlanRunner
 from oracle import inputs as I
-from oracle.check import TOL_BF16, max_rel_err
+from oracle.check import TOL_BF16, max_rel_err, assert_parity
 
 from lighthouse_b200.ingress.torch import CudaBackend, JITFunction, UnsupportedGraph, gpu_backend, import_fx_graph
 
@@ -84,7 +84,7 @@ def test_mlp_graph_becomes_two_fused_gemms_and_matches_eager():
     assert plan.ops[-1].operands[0].slot == len(inputs)  # the last GEMM writes the result buffer itself
     assert results[0].dtype == torch.bfloat16 and results[0].shape == [48, 32]
     (got,) = interpret(plan, results, inputs)
-    assert max_rel_err(got, want.float().numpy()) <= TOL_BF16
+    assert_parity(got, want.float().numpy(), "bf16")
 
 
 def test_decoder_block_graph_matches_eager():
@@ -96,7 +96,7 @@ def test_decoder_block_graph_matches_eager():
     attn = next(op for op in plan.ops if op.kind == "attention")
     assert attn.attrs["causal"] and attn.operands[1].shape == (2, 2, 32, 64)  # strided (B, H, S, hs) views, no copies
     (got,) = interpret(plan, results, inputs)
-    assert max_rel_err(got, want.float().numpy()) <= TOL_BF16
+    assert_parity(got, want.float().numpy(), "bf16")
 
 
 def test_two_results_and_f32_graph():
@@ -111,7 +111,7 @@ def test_two_results_and_f32_graph():
     assert [tuple(s.shape) for s in plan.args[-2:]] == [(24, 16), (24, 16)]
     got = interpret(plan, results, inputs)
     for g, w in zip(got, want):
-        assert max_rel_err(g, w.numpy()) <= 1e-5
+        assert_parity(g, w.numpy(), "f32")
 
 
 def test_embedding_rms_norm_and_split_views():
@@ -135,7 +135,7 @@ def test_embedding_rms_norm_and_split_views():
     kinds = plan.kinds()
     assert "embedding" in kinds and "rmsnorm" in kinds and kinds.count("gemm") == 2
     (got,) = interpret(plan, results, inputs)
-    assert max_rel_err(got, want.float().numpy()) <= TOL_BF16
+    assert_parity(got, want.float().numpy(), "bf16")
 
 
 def test_unsupported_graphs_are_value_errors_and_nothing_runs_on_cpu():
@@ -181,7 +181,7 @@ def test_torch_compile_on_the_cuda_backend_matches_eager(ctx):
             want = model(x)
             got = torch.compile(model, backend=recording_backend, dynamic=False)(x)
         torch.cuda.synchronize()
-        assert max_rel_err(got.float().cpu().numpy(), want.float().cpu().numpy()) <= TOL_BF16
+        assert_parity(got.float().cpu().numpy(), want.float().cpu().numpy(), "bf16")
         jit = backend._last_jit_function
         assert jit is not None and jit.plan.kinds().count("gemm") >= 2
         times = jit.benchmark(*seen["inputs"], nruns=3, nwarmup=1)  # parameters and inputs in graph order

@@ -8,15 +8,20 @@ keeps the scores in a 4 MiB buffer that ships inside the library instead.
 
 The test calls it through the C ABI twice in a row (the buffer still holds the first call's
 scores when the second one starts) and checks both results against the existing entry point,
-``lh_b200_attention_fwd``, on the same f32 inputs (which also takes the un-fused route).
-The file name makes pytest collect it last, so a run that stops at the first failure has
-already been through every other test.
+``lh_b200_attention_fwd``, on the same f32 inputs (which also takes the un-fused route), and
+against the CPU oracle's attention, so the arithmetic is not only compared with itself. The
+second call is also watched for allocation: the free device memory the driver reports must be
+the same before and after it. The file name makes pytest collect it last, so a run that stops
+at the first failure has already been through every other test.
 """
 
 import ctypes
 
 import pytest
 import torch
+
+from oracle import reference_ops as R
+from oracle.check import assert_parity
 
 from lighthouse_b200 import _native as N
 from lighthouse_b200.context import as_memref
@@ -37,8 +42,9 @@ def call_noalloc(ctx, o, q, k, v, scale, causal):
 
 def test_noalloc_attention_matches_existing_entry_point_twice(ctx):
     g = torch.Generator().manual_seed(21)
-    shapes = [((2, 4, 96, 32), (2, 2, 160, 32), True), ((1, 3, 200, 64), (1, 3, 200, 64), False)]
-    for (qs, ks, causal) in shapes:  # two calls in a row, second one on a dirty buffer
+    # key lengths that are and are not multiples of 8; grouped heads; both mask settings
+    shapes = [((2, 4, 96, 32), (2, 2, 160, 32), True), ((1, 3, 200, 64), (1, 3, 203, 64), False), ((1, 2, 77, 16), (1, 1, 77, 16), True)]
+    for n, (qs, ks, causal) in enumerate(shapes):  # calls in a row, later ones on a dirty buffer
         q = torch.randn(*qs, generator=g).cuda()
         k = torch.randn(*ks, generator=g).cuda()
         v = torch.randn(*ks, generator=g).cuda()
@@ -47,10 +53,15 @@ def test_noalloc_attention_matches_existing_entry_point_twice(ctx):
         ctx.attention_fwd(want, q, k, v, scale, causal)
         ctx.sync()
         got = torch.full_like(q, float("nan"))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = call_noalloc(ctx, got, q, k, v, scale, causal)
         assert rc == N.LH_OK, ctx._lib.lh_b200_last_error(ctx.handle)
         ctx.sync()
+        if n > 0:  # the first call on a device is the documented warm-up
+            assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
         assert rel_err(got, want) <= TOL_F32
+        assert_parity(got.cpu().numpy(), R.attention_unfused_f32(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy(), scale=scale, causal=causal), "f32")
     # bf16 inputs work too (compared with the same op sequence on the existing path is not
     # possible there — bf16 goes to the fused kernel — so compare against the f32 result)
     qb, kb, vb = q.bfloat16(), k.bfloat16(), v.bfloat16()
@@ -60,6 +71,7 @@ def test_noalloc_attention_matches_existing_entry_point_twice(ctx):
     assert call_noalloc(ctx, out, qb, kb, vb, scale, causal) == N.LH_OK
     ctx.sync()
     assert rel_err(out.float(), ref) <= 2e-2
+    assert_parity(out.float().cpu().numpy(), R.attention(qb.float().cpu().numpy(), kb.float().cpu().numpy(), vb.float().cpu().numpy(), scale=scale, causal=causal, io_dtype="bf16"), "bf16")
 
 
 def test_noalloc_attention_rejects_sizes_beyond_its_buffer(ctx):
@@ -71,3 +83,9 @@ def test_noalloc_attention_rejects_sizes_beyond_its_buffer(ctx):
     assert "exceeds" in msg and "1048576" in msg
     bad = torch.zeros(1, 2, 8, 16, device="cuda")
     assert call_noalloc(ctx, o, q, bad, bad, 0.25, False) != N.LH_OK  # 1 query head, 2 kv heads
+    # f16 operands are refused before anything is launched: the result buffer stays as it was
+    h = torch.zeros(1, 1, 8, 16, device="cuda", dtype=torch.float16)
+    oh = torch.full((1, 1, 8, 16), 3.0, device="cuda")
+    launches = ctx.launch_count
+    assert call_noalloc(ctx, oh, h, h, h, 0.25, False) == N.LH_ERR_UNSUPPORTED
+    assert ctx.launch_count == launches and float(oh.min()) == 3.0
