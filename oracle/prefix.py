@@ -40,7 +40,7 @@ def llama_prefix_reference(weights: dict, x, cfg, sequences=(0, 1), prefix: int 
     chosen sequences of ``x`` ((batch * seq, dim), torch bf16 or numpy); ``weights`` in the
     reference's (out, in) layout as ``workloads.synthetic.llama_weights`` makes them."""
     xs = to_np(x).reshape(cfg.batch, cfg.seq, cfg.dim)[list(sequences), :prefix]
-    out = R.llama_forward(xs, _LazyLayers(weights["layers"]), to_np(weights["norm"]), cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True)
+    out = R.llama_forward(xs, _LazyLayers(weights["layers"]), to_np(weights["norm"]), cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True, fused_residual=True)
     return out.reshape(len(sequences) * prefix, cfg.dim)
 
 

@@ -34,13 +34,20 @@ def native_lib():
 
 @pytest.fixture(scope="session")
 def ctx(native_lib):
-    """Launches on torch's current stream: the tests build operands and fill result buffers
+    """Launches on the stream torch uses: the tests build operands and fill result buffers
     with torch ops, and stream order is what makes a kernel see them (the context's own
-    stream is non-blocking and would need explicit synchronisation on both sides)."""
+    stream is non-blocking and would need explicit synchronisation on both sides). That
+    stream is a created one, made torch's current stream for the whole session, because the
+    legacy default stream cannot be captured into a CUDA graph."""
+    import torch
+
     from lighthouse_b200.context import CudaContext
 
+    stream = torch.cuda.Stream(device=0)
+    torch.cuda.set_stream(stream)
     c = CudaContext(0, use_torch_stream=True)
     yield c
+    torch.cuda.synchronize()
     c.close()
 
 

@@ -32,7 +32,7 @@ def gpt_reference(cfg, w, ids):
 def llama_reference(cfg, w, x):
     wn = I.tree_to_np(w)
     xr = I.to_np(x).reshape(cfg.batch, cfg.seq, cfg.dim)
-    out = R.llama_forward(xr, wn["layers"], wn["norm"], cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True)
+    out = R.llama_forward(xr, wn["layers"], wn["norm"], cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True, fused_residual=True)
     return out.reshape(cfg.tokens, cfg.dim)
 
 

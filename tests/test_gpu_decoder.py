@@ -65,7 +65,7 @@ def test_llama_forward_matches_oracle(ctx):
     x = torch.randn(cfg.tokens, cfg.dim, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
     out = run_llama(ctx, cfg, w, x)
     wn = I.tree_to_np(w)
-    ref = R.llama_forward(I.to_np(x).reshape(cfg.batch, cfg.seq, cfg.dim), wn["layers"], wn["norm"], cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True)
+    ref = R.llama_forward(I.to_np(x).reshape(cfg.batch, cfg.seq, cfg.dim), wn["layers"], wn["norm"], cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True, fused_residual=True)
     assert_parity(out.float().cpu().numpy(), ref.reshape(cfg.tokens, cfg.dim), "bf16")
 
 

@@ -135,7 +135,7 @@ def test_two_ranks_on_two_gpus_match_the_oracle():
     w = I.llama_weights(cfg.n_layer, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.ffn, seed=7, std=0.05)
     x = torch.randn(cfg.tokens, cfg.dim, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
     wn = I.tree_to_np(w)
-    ref = R.llama_forward(I.to_np(x).reshape(cfg.batch, cfg.seq, cfg.dim), wn["layers"], wn["norm"], cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True)
+    ref = R.llama_forward(I.to_np(x).reshape(cfg.batch, cfg.seq, cfg.dim), wn["layers"], wn["norm"], cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True, fused_residual=True)
     ref = ref.reshape(cfg.tokens, cfg.dim)
     for name in ("allreduce", "nccl_overlapped", "fused_overlapped"):
         for r in results:

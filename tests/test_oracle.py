@@ -70,7 +70,7 @@ def test_llama_stack_matches_reference_model(llama_golden):
     layers = [{k: g[f"tf_l{i}_{k}"] for k in keys} for i in range(nl)]
     assert_close(R.llama_block(g["tf_x"], layers[0], nh, nkv, 10000.0, 1e-5, "f32"), g["tf_block0_out"], "f32", "TransformerBlock")
     assert_close(R.llama_forward(g["tf_x"], layers, g["tf_norm"], nh, nkv, 10000.0, 1e-5, "f32"), g["tf_out"], "f32", "Transformer trunk")
-    assert_close(R.llama_forward(g["tf_x"], layers, g["tf_norm"], nh, nkv, 10000.0, 1e-5, "f32", fused_swiglu=True), g["tf_out"], "f32", "fused SwiGLU")
+    assert_close(R.llama_forward(g["tf_x"], layers, g["tf_norm"], nh, nkv, 10000.0, 1e-5, "f32", fused_swiglu=True, fused_residual=True), g["tf_out"], "f32", "fused SwiGLU and residual")
 
 
 def test_row_ops_match_torch():
@@ -209,7 +209,7 @@ def test_causal_prefix_property_of_the_decoder_oracles():
     w = I.llama_weights(cfg.n_layer, cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.ffn, seed=5, std=0.1)
     x = torch.randn(cfg.tokens, cfg.dim, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
     wn = I.tree_to_np(w)
-    full = R.llama_forward(I.to_np(x).reshape(cfg.batch, cfg.seq, cfg.dim), wn["layers"], wn["norm"], cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True)
+    full = R.llama_forward(I.to_np(x).reshape(cfg.batch, cfg.seq, cfg.dim), wn["layers"], wn["norm"], cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True, fused_residual=True)
     rows = P.prefix_rows(cfg.seq, (0, 2), 9)
     got = P.llama_prefix_reference(w, x, cfg, (0, 2), 9)
     assert max_rel_err(got, full.reshape(cfg.tokens, cfg.dim)[rows]) <= 1e-6
