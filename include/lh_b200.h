@@ -120,6 +120,15 @@ int64_t lh_b200_launch_count(lh_ctx_t* ctx);
 /* Device properties the host side needs: SM count, and whether the device is sm_100. */
 int lh_b200_device_info(lh_ctx_t* ctx, int* sm_count, int* cc_major, int* cc_minor);
 
+/* Runs one small kernel whose 64 waits can never be satisfied (an mbarrier nothing arrives on,
+ * a flag in this GPU's own memory nothing writes) through the bounded-wait helpers every kernel
+ * of this library uses, with `limit_ns` (at most 100 ms) as their limit. The kernel returns
+ * normally once the waits have given up; `timed_out_waits` receives how many did (64). The
+ * context's status word then holds the self-test's code, so the NEXT lh_b200_sync returns
+ * LH_ERR_DEVICE once and clears it; the context stays usable. This is how the give-up path
+ * is exercised without making any GPU hang or fault. No counterpart in the reference. */
+int lh_b200_selftest_bounded_wait(lh_ctx_t* ctx, uint64_t limit_ns, int* timed_out_waits);
+
 /* ------------------------------------------------------------------- memory */
 /* Device buffers for the DeviceMemoryManager protocol
  * (lighthouse/execution/memory_manager.py:70-85,89-168: alloc / copy / dealloc). */

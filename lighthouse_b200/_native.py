@@ -135,6 +135,7 @@ _PROTOTYPES = {
     "lh_b200_last_error": (c_char_p, [c_void_p]),
     "lh_b200_launch_count": (c_int64, [c_void_p]),
     "lh_b200_device_info": (c_int, [c_void_p, POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
+    "lh_b200_selftest_bounded_wait": (c_int, [c_void_p, ctypes.c_uint64, POINTER(c_int)]),
     "lh_b200_malloc": (c_int, [c_void_p, c_size_t, POINTER(c_void_p)]),
     "lh_b200_free": (c_int, [c_void_p, c_void_p]),
     "lh_b200_memcpy": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int]),

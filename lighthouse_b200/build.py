@@ -23,7 +23,7 @@ OBJ_DIR = LIB_DIR / "obj"
 LIB_PATH = LIB_DIR / "liblh_b200.so"
 INCLUDE = PKG_DIR.parent / "include"
 
-SOURCES = ["api.cu", "gemm_tc.cu", "gemm_simt.cu", "attention_tc.cu", "attention_tc2.cu", "rowops.cu", "fused_collective.cu"]
+SOURCES = ["api.cu", "gemm_tc.cu", "gemm_simt.cu", "attention_tc2.cu", "attention_tc3.cu", "rowops.cu", "fused_collective.cu", "selftest.cu"]
 
 NVCC_FLAGS = [
     "-gencode",

@@ -105,6 +105,13 @@ class CudaContext:
     def sync(self) -> None:
         N.check(self._lib.lh_b200_sync(self.handle), self.handle, "lh_b200_sync")
 
+    def selftest_bounded_wait(self, limit_ns: int = 1_000_000) -> int:
+        """Lets 64 bounded waits run out on purpose (``lh_b200_selftest_bounded_wait``); returns
+        how many gave up. The next ``sync()`` raises once, then the context is usable again."""
+        n = c_int()
+        N.check(self._lib.lh_b200_selftest_bounded_wait(self.handle, int(limit_ns), byref(n)), self.handle, "lh_b200_selftest_bounded_wait")
+        return n.value
+
     @property
     def launch_count(self) -> int:
         return int(self._lib.lh_b200_launch_count(self.handle))

@@ -1,8 +1,7 @@
-// Flash-attention forward, second-generation kernel: P stays in tensor memory.
+// Flash-attention forward, one query tile per CTA, P kept in tensor memory.
 //
-// Same algorithm and numerics as attention_tc.cu (online softmax of
-// replace_with_fused_attention.py:334-455 in the reference: f32 scores / max / sum /
-// accumulator, P rounded to bf16 before P.V, O = acc / l). What changes is the data path:
+// Online softmax of replace_with_fused_attention.py:334-455 in the reference: f32 scores /
+// max / sum / accumulator, P rounded to bf16 before P.V, O = acc / l. The data path:
 //   * the softmax warps write P (bf16 pairs) back into the tensor-memory columns the scores
 //     came from, and the second MMA reads its A operand from tensor memory, so P never
 //     crosses shared memory and the P.V product loads only V from it;

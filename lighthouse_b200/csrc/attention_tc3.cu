@@ -1,0 +1,473 @@
+// Flash-attention forward, third-generation kernel: two query tiles per CTA in explicit
+// ping-pong, one CTA per SM.
+//
+// Algorithm and numerics are those of attention_tc2.cu (online softmax of
+// replace_with_fused_attention.py:334-455 in the reference: f32 scores / max / sum /
+// accumulator, P rounded to bf16 before P.V, O = acc / l; P kept in tensor memory over the
+// score columns, TS-form MMA). What changes is who overlaps with whom. Two independent CTAs on
+// an SM run in phase: their MMAs share the tensor pipe at instruction granularity, so both
+// score tiles complete together, both softmaxes then share the special-function unit, and each
+// pipe idles while the other works (measured: tensor pipe 44 %, special-function pipe 45 %
+// busy, never together). Here ONE MMA warp serves two query tiles A and B of the same
+// (batch, head) and fixes the order
+//     ... P_A V -> Q_A K' -> P_B V -> Q_B K' -> P_A' V' -> ...
+// so that tile A's softmax runs exactly under tile B's two products and vice versa, and both
+// tiles read the same K / V tiles from shared memory (loaded once for 256 query rows).
+//
+// Warps: 0 TMA producer (Q_A, Q_B once; K and V in two-stage rings), 1 MMA issuer, 2-5 softmax
+// of tile A, 6-9 softmax of tile B (one row per thread). Tensor memory: S_A, S_B, O_A, O_B,
+// 128 columns each = all 512. Every wait is bounded.
+#include "common.cuh"
+#include "epilogue.cuh"
+#include "ptx.cuh"
+#include <stdlib.h>
+
+namespace lh {
+
+namespace {
+
+constexpr int BQ3 = 128;   // query rows per tile; two tiles per CTA
+constexpr int BKV3 = 128;
+constexpr int ATT3_THREADS = 320;
+constexpr int SUBTILE3 = 128 * 128;  // 128 rows x 64 bf16
+
+struct Attn3Params {
+  int B, Hq, Hkv, Sq, Skv;
+  void* O;
+  int o_dtype;
+  int64_t sob, soh, sos;
+  float scale_log2;
+  int causal;
+  int num_q_pairs;
+  int* dev_status;
+};
+
+template <int HD>
+struct Attn3Smem {
+  static constexpr int Q_BYTES = BQ3 * HD * 2;   // one query tile
+  static constexpr int KV_BYTES = BKV3 * HD * 2;
+  static constexpr int Q_OFF = 0;                      // tiles A, B
+  static constexpr int K_OFF = Q_OFF + 2 * Q_BYTES;    // 2 stages
+  static constexpr int V_OFF = K_OFF + 2 * KV_BYTES;   // 2 stages
+  static constexpr int BAR_OFF = V_OFF + 2 * KV_BYTES;
+  static constexpr int NUM_BARS = 17;
+  static constexpr int DYN_BYTES = BAR_OFF + NUM_BARS * 8 + 16 + 1024;
+  static_assert(DYN_BYTES <= 232448, "exceeds the shared memory a CTA can opt into");
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ bool wait_warp3(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* dev_status, int code) {
+  // every lane observes the phase itself (its later reads are ordered after it); the warp
+  // agrees on the verdict so that a timeout never splits it
+  const bool ok = mbar_wait(bar, parity, abort_flag, dev_status, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
+// Key tiles a query tile starting at row q0 visits (0 if the tile lies outside the queries).
+__device__ __forceinline__ int kv_tiles_for(const Attn3Params& p, int q0) {
+  if (q0 >= p.Sq) return 0;
+  int n = (p.Skv + BKV3 - 1) / BKV3;
+  if (p.causal) {
+    const int last_col = min(q0 + BQ3 - 1 + (p.Skv - p.Sq), p.Skv - 1);
+    n = min(n, max(last_col, 0) / BKV3 + 1);
+  }
+  return n;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(ATT3_THREADS, 1)
+attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const Attn3Params p) {
+  using L = Attn3Smem<HD>;
+  constexpr int TMEM_COLS = 512;
+  constexpr uint32_t S_COL = 0, O_COL = 256;  // tile t: scores at S_COL + 128 t, accumulator at O_COL + 128 t
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;    // [2] stages
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;    // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;    // [2] tiles
+  uint64_t* p_half = bars + 11;   // [tile][half]: keys [0,64) / [64,128) of P written
+  uint64_t* pv_done = bars + 15;  // [2] tiles
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // Work order: a causal pair of query tiles (2i, 2i + 1) visits up to 2i + 2 key tiles, so
+  // pairs are handed out heaviest first and the tail of the grid is made of short blocks.
+  int bh, qp;
+  if (p.causal) {
+    const int nbh = gridDim.x / p.num_q_pairs;
+    qp = p.num_q_pairs - 1 - blockIdx.x / nbh;
+    bh = blockIdx.x % nbh;
+  } else {
+    bh = blockIdx.x / p.num_q_pairs;
+    qp = blockIdx.x % p.num_q_pairs;
+  }
+  const int b = bh / p.Hq;
+  const int hq = bh % p.Hq;
+  const int hkv = hq / (p.Hq / p.Hkv);
+  const int q0 = qp * (2 * BQ3);
+  const int offset = p.Skv - p.Sq;
+  const int n_a = kv_tiles_for(p, q0), n_b = kv_tiles_for(p, q0 + BQ3);
+  const int n_max = max(n_a, n_b);
+  auto n_of = [&](int t) { return t == 0 ? n_a : n_b; };
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_half[2 * s], 128);
+      mbar_init(&p_half[2 * s + 1], 128);
+      mbar_init(&pv_done[s], 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      // Both query tiles; rows beyond the queries arrive as zeros (their results are never stored).
+      mbar_arrive_expect_tx(q_full, 2 * L::Q_BYTES);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int h = 0; h < HD / 64; ++h)
+          tma_load_4d(smem + L::Q_OFF + t * L::Q_BYTES + h * SUBTILE3, &tmQ, q_full, h * 64, q0 + t * BQ3, hq, b);
+      for (int j = 0; j < n_max; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1u;
+        if (!mbar_wait(&k_empty[st], ph ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_PRODUCER)) break;
+        mbar_arrive_expect_tx(&k_full[st], L::KV_BYTES);
+#pragma unroll
+        for (int h = 0; h < HD / 64; ++h)
+          tma_load_4d(smem + L::K_OFF + st * L::KV_BYTES + h * SUBTILE3, &tmK, &k_full[st], h * 64, j * BKV3, hkv, b);
+        if (!mbar_wait(&v_empty[st], ph ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_PRODUCER)) break;
+        mbar_arrive_expect_tx(&v_full[st], L::KV_BYTES);
+#pragma unroll
+        for (int h = 0; h < HD / 64; ++h)
+          tma_load_4d(smem + L::V_OFF + st * L::KV_BYTES + h * SUBTILE3, &tmV, &v_full[st], h * 64, j * BKV3, hkv, b);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc(UMMA_BF16, BQ3, BKV3, false, false);
+      constexpr uint32_t idesc_pv = make_idesc(UMMA_BF16, BQ3, HD, false, true);
+      const uint32_t q_addr = smem_u32(smem + L::Q_OFF);
+      const uint32_t k_addr = smem_u32(smem + L::K_OFF);
+      const uint32_t v_addr = smem_u32(smem + L::V_OFF);
+      // S_t = Q_t K_j^T into tile t's score columns
+      auto issue_qk = [&](int t, int j) {
+        const uint32_t qa = q_addr + t * L::Q_BYTES, ka = k_addr + (j & 1) * L::KV_BYTES;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k / 4) * SUBTILE3 + (k % 4) * 32;
+          umma_f16_ss(tmem_base + S_COL + t * 128, make_smem_desc_sw128(qa + off, 16, 1024), make_smem_desc_sw128(ka + off, 16, 1024), idesc_qk,
+                      k != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[t]);
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.dev_status, DEV_TIMEOUT_MMA);
+      if (ok && n_max > 0) {
+        ok = mbar_wait(&k_full[0], 0, abort_flag, p.dev_status, DEV_TIMEOUT_MMA);
+        if (ok) {
+          tc_fence_after_sync();
+          for (int t = 0; t < 2; ++t)
+            if (n_of(t) > 0) issue_qk(t, 0);
+          umma_commit(&k_empty[0]);
+        }
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1u;   // phase of the K / V stage
+        const uint32_t tph = j & 1u;         // phase of the per-tile barriers
+        const bool have_next = j + 1 < n_max;
+        if (!mbar_wait(&v_full[st], ph, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) break;
+        bool next_k_seen = false;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j < n_of(t)) {
+            // O_t += P_t V_j, P_t read from tensor memory, its first 64 keys consumed while the
+            // softmax warps still produce the rest
+            const uint32_t va = v_addr + st * L::KV_BYTES;
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              if (!mbar_wait(&p_half[2 * t + hf], tph, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+#pragma unroll
+              for (int k = hf * 4; k < hf * 4 + 4; ++k) {
+                // 16 keys of P = 8 packed columns; V rows are keys, 64 head-dim elements per 128-byte row
+                umma_f16_ts(tmem_base + O_COL + t * 128, tmem_base + S_COL + t * 128 + k * 8, make_smem_desc_sw128(va + k * 2048, SUBTILE3, 1024),
+                            idesc_pv, (j | k) != 0 ? 1u : 0u);
+              }
+            }
+            if (!ok) break;
+            umma_commit(&pv_done[t]);
+          }
+          if (j + 1 < n_of(t)) {
+            // The next scores of this tile overwrite the columns the product just issued reads P
+            // from; the tensor core runs this thread's MMAs in issue order.
+            if (!next_k_seen) {
+              if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+              next_k_seen = true;
+            }
+            issue_qk(t, j + 1);
+          }
+        }
+        if (!ok) break;
+        umma_commit(&v_empty[st]);                          // both tiles' P V of this stage are issued
+        if (have_next) umma_commit(&k_empty[(j + 1) & 1]);  // and both tiles' Q K^T on the next K
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax
+    const int t = (warp - 2) >> 2;  // which query tile this warp group serves
+    const int quarter = warp & 3;   // tensor-memory lanes [32 quarter, +32) are this warp's
+    const int row = quarter * 32 + lane;
+    const int q0t = q0 + t * BQ3;
+    const int q_row = q0t + row;
+    const int n_mine = n_of(t);
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_base + S_COL + t * 128 + lane_off;
+    const uint32_t o_addr = tmem_base + O_COL + t * 128 + lane_off;
+    uint64_t* my_s_full = &s_full[t];
+    uint64_t* my_p_half = &p_half[2 * t];
+    float m_used = -INFINITY;
+    float l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_mine; ++j) {
+      if (!wait_warp3(my_s_full, j & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_SOFTMAX)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int col0 = j * BKV3;
+      const bool need_mask = (col0 + BKV3 > p.Skv) || (p.causal && (col0 + BKV3 - 1 > q0t + offset));
+      const int limit = need_mask ? (p.causal ? min(p.Skv - 1, q_row + offset) : (p.Skv - 1)) - col0 : BKV3;  // last visible column in this tile
+      // pass 1: row max of the scores, two 32-column loads in flight at a time
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;  // independent chains
+#pragma unroll
+      for (int c = 0; c < 4; c += 2) {
+        uint32_t s0[32], s1[32];
+        tmem_ld_32x32b_x32(s_addr + c * 32, s0);
+        tmem_ld_32x32b_x32(s_addr + c * 32 + 32, s1);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (c * 32 + i > limit) s0[i] = 0xff800000u;  // -inf
+            if (c * 32 + 32 + i > limit) s1[i] = 0xff800000u;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          mx0 = fmax3(mx0, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(s0[i + 2]), __uint_as_float(s0[i + 3]));
+          mx2 = fmax3(mx2, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+          mx3 = fmax3(mx3, __uint_as_float(s1[i + 2]), __uint_as_float(s1[i + 3]));
+        }
+      }
+      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      mx *= p.scale_log2;  // scale > 0: max commutes with the scaling
+      // lazy rescale: move the reference max only when it grew by more than 8 (2^8 headroom)
+      float alpha = 1.f;
+      const bool need = (mx > m_used + 8.f) || (m_used == -INFINITY && mx > -INFINITY);
+      if (need) {
+        alpha = (m_used == -INFINITY) ? 0.f : ex2_approx(m_used - mx);
+        m_used = mx;
+      }
+      const bool warp_need = __any_sync(0xffffffffu, need);
+      if (j > 0 && warp_need) {
+        // s_full(j) fired after every MMA issued before it, this tile's P V of key tile j - 1
+        // included: the accumulator is up to date and nothing writes it until P(j) is handed over
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(o_addr + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32b_x32(o_addr + c * 32, o);
+        }
+      }
+      // pass 2: P = exp2(scale*S - m), row sum, bf16 pairs written over the S columns; each
+      // half (64 keys) is handed to the MMA warp as soon as it is in tensor memory
+      const float msub = (m_used == -INFINITY) ? 0.f : m_used;
+      float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t s0[32], s1[32];
+        tmem_ld_32x32b_x32(s_addr + hf * 64, s0);
+        tmem_ld_32x32b_x32(s_addr + hf * 64 + 32, s1);
+        tmem_ld_wait();
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = ex2_approx(fmaf(__uint_as_float(s0[2 * i]), p.scale_log2, -msub));
+          float p1 = ex2_approx(fmaf(__uint_as_float(s0[2 * i + 1]), p.scale_log2, -msub));
+          float p2 = ex2_approx(fmaf(__uint_as_float(s1[2 * i]), p.scale_log2, -msub));
+          float p3 = ex2_approx(fmaf(__uint_as_float(s1[2 * i + 1]), p.scale_log2, -msub));
+          if (need_mask) {
+            const int cbase = hf * 64 + 2 * i;
+            p0 = (cbase <= limit) ? p0 : 0.f;
+            p1 = (cbase + 1 <= limit) ? p1 : 0.f;
+            p2 = (cbase + 32 <= limit) ? p2 : 0.f;
+            p3 = (cbase + 33 <= limit) ? p3 : 0.f;
+          }
+          rs0 += p0;
+          rs1 += p1;
+          rs2 += p2;
+          rs3 += p3;
+          pk[i] = pack_bf16x2(p0, p1);
+          pk[16 + i] = pack_bf16x2(p2, p3);
+        }
+        tmem_st_32x32b_x32(s_addr + hf * 32, pk);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        mbar_arrive(&my_p_half[hf]);
+      }
+      l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
+    }
+    if (ok && n_mine > 0 && wait_warp3(&pv_done[t], (n_mine - 1) & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_SOFTMAX)) {
+      tc_fence_after_sync();
+      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+      char* obase = static_cast<char*>(p.O);
+      const int64_t oidx = static_cast<int64_t>(b) * p.sob + static_cast<int64_t>(hq) * p.soh + static_cast<int64_t>(q_row) * p.sos;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(o_addr + c * 32, o);
+        tmem_ld_wait();
+        if (q_row < p.Sq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(o[g * 8 + i]) * inv_l;
+            store8_from_f32(obase, p.o_dtype, oidx + c * 32 + g * 8, v);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    if (*abort_flag) {
+      // a role gave up: let copies and MMAs already in flight drain before the tensor memory
+      // goes back to the allocator
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int HD>
+int launch3_hd(lh_ctx* ctx, const AttnProblem& a) {
+  using L = Attn3Smem<HD>;
+  CUtensorMap tmQ, tmK, tmV;
+  const uint32_t box[4] = {64, 128, 1, 1};
+  {
+    const uint64_t dims[4] = {(uint64_t)a.D, (uint64_t)a.Sq, (uint64_t)a.Hq, (uint64_t)a.B};
+    const uint64_t st[3] = {(uint64_t)a.sqs * 2, (uint64_t)a.sqh * 2, (uint64_t)a.sqb * 2};
+    int rc = encode_tensor_map(ctx, &tmQ, LH_BF16, 4, const_cast<void*>(a.Q), dims, st, box, 1);
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[4] = {(uint64_t)a.D, (uint64_t)a.Skv, (uint64_t)a.Hkv, (uint64_t)a.B};
+    const uint64_t stk[3] = {(uint64_t)a.sks * 2, (uint64_t)a.skh * 2, (uint64_t)a.skb * 2};
+    const uint64_t stv[3] = {(uint64_t)a.svs * 2, (uint64_t)a.svh * 2, (uint64_t)a.svb * 2};
+    int rc = encode_tensor_map(ctx, &tmK, LH_BF16, 4, const_cast<void*>(a.K), dims, stk, box, 1);
+    if (rc) return rc;
+    rc = encode_tensor_map(ctx, &tmV, LH_BF16, 4, const_cast<void*>(a.V), dims, stv, box, 1);
+    if (rc) return rc;
+  }
+  Attn3Params p;
+  p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.Sq = a.Sq; p.Skv = a.Skv;
+  p.O = a.O; p.o_dtype = a.o_dtype; p.sob = a.sob; p.soh = a.soh; p.sos = a.sos;
+  p.scale_log2 = a.scale * 1.44269504088896340736f;
+  p.causal = a.causal;
+  p.num_q_pairs = (a.Sq + 2 * BQ3 - 1) / (2 * BQ3);
+  p.dev_status = ctx->dev_status;
+  auto kernel = attn_fwd_tc3_kernel<HD>;
+  LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+  const int64_t grid = static_cast<int64_t>(a.B) * a.Hq * p.num_q_pairs;
+  kernel<<<static_cast<unsigned>(grid), ATT3_THREADS, L::DYN_BYTES, ctx->stream>>>(tmQ, tmK, tmV, p);
+  LH_CHECK_LAUNCH(ctx, "attn_fwd_tc3_kernel");
+  return LH_OK;
+}
+
+}  // namespace
+
+int attn_tc3_launch(lh_ctx* ctx, const AttnProblem& a) {
+  if (a.scale <= 0.f) return set_error(ctx, LH_ERR_UNSUPPORTED, "attention: scale must be positive");
+  if (a.D == 128) return launch3_hd<128>(ctx, a);
+  return launch3_hd<64>(ctx, a);
+}
+
+// What the tensor-core kernels take: bf16 Q / K / V with unit stride in the head dimension,
+// head sizes 64 and 128, 16-byte aligned rows (tensor maps), grouped heads, and for a causal
+// mask at least as many keys as queries.
+int attn_tc_supported(const lh_ctx* ctx, const AttnProblem& a) {
+  if (ctx->cc_major != 10) return 0;
+  if (a.dtype != LH_BF16) return 0;
+  if (a.o_dtype != LH_BF16 && a.o_dtype != LH_F32) return 0;
+  if (a.D != 64 && a.D != 128) return 0;
+  if (a.Hkv < 1 || a.Hq % a.Hkv) return 0;
+  if (a.causal && a.Skv < a.Sq) return 0;
+  if (a.scale <= 0.f) return 0;
+  auto ok8 = [](int64_t s) { return (s % 8) == 0; };
+  if (!ok8(a.sqb) || !ok8(a.sqh) || !ok8(a.sqs) || !ok8(a.skb) || !ok8(a.skh) || !ok8(a.sks) || !ok8(a.svb) ||
+      !ok8(a.svh) || !ok8(a.svs) || !ok8(a.sob) || !ok8(a.soh) || !ok8(a.sos))
+    return 0;
+  auto al = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+  if (!al(a.Q) || !al(a.K) || !al(a.V) || !al(a.O)) return 0;
+  if (static_cast<int64_t>(a.B) * a.Hq * ((a.Sq + BQ3 - 1) / BQ3) > 0x7fffffffLL) return 0;
+  return 1;
+}
+
+int attn_tc_launch(lh_ctx* ctx, const AttnProblem& a) {
+  // One query tile per (batch, head): nothing to ping-pong with, two independent blocks per SM
+  // serve such problems better.
+  static const int pick = getenv("LH_ATTN_KERNEL") ? atoi(getenv("LH_ATTN_KERNEL")) : 0;  // experiment switch (development only)
+  if (pick == 2 || (pick == 0 && a.Sq <= BQ3)) return attn_tc2_launch(ctx, a);
+  return attn_tc3_launch(ctx, a);
+}
+
+}  // namespace lh

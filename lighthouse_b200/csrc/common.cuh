@@ -163,6 +163,7 @@ struct AttnProblem {
 int attn_tc_supported(const lh_ctx* ctx, const AttnProblem& p);
 int attn_tc_launch(lh_ctx* ctx, const AttnProblem& p);
 int attn_tc2_launch(lh_ctx* ctx, const AttnProblem& p);
+int attn_tc3_launch(lh_ctx* ctx, const AttnProblem& p);
 int attn_simt_launch(lh_ctx* ctx, const AttnProblem& p);
 
 // ------------------------------------------------------------ row operators

@@ -29,7 +29,6 @@ constexpr int RNG_ROWS = 8;  // rows a block keeps in flight
 // with a GEMM block (which takes nearly all of the SM's shared memory), so the two kernels
 // split the GPU cleanly by SMs instead of delaying some of each other's blocks.
 constexpr int RNG_SMEM_FENCE = 40 * 1024;  // + the static arrays stays under the 48 KB a kernel gets without opting in
-constexpr int DEV_TIMEOUT_PEER = 106;
 
 struct RngParams {
   const char* part;   // my rows of the partial sums: multicast address (MC) or local; null = no reduce
@@ -91,22 +90,9 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 // Waits until flag `slot` of every rank in the local pad has reached `epoch`. Threads
 // 0..world-1 poll one flag each. Returns false (for the whole block) after the time limit.
 __device__ bool wait_all_ranks(const RngParams& p, int slot, int* s_abort) {
-  if (threadIdx.x < p.world) {
-    const uint32_t* flag = p.pads[p.rank] + slot * LH_MAX_RANKS + threadIdx.x;
-    const uint64_t t0 = global_timer_ns();
-    uint32_t spins = 0;
-    // epochs are compared as signed distances so that a wrap of the 32-bit counter is harmless
-    while (static_cast<int32_t>(ld_acquire_sys(flag) - p.epoch) < 0) {
-      if (((++spins) & 0x3fu) == 0u) {
-        if (*reinterpret_cast<volatile int*>(s_abort)) break;
-        if (global_timer_ns() - t0 > LH_WAIT_TIMEOUT_NS) {
-          *reinterpret_cast<volatile int*>(s_abort) = 1;
-          if (p.dev_status) atomicCAS(p.dev_status, 0, DEV_TIMEOUT_PEER);
-          break;
-        }
-      }
-    }
-  }
+  if (threadIdx.x < p.world)
+    flag_wait_limit(p.pads[p.rank] + slot * LH_MAX_RANKS + threadIdx.x, p.epoch, reinterpret_cast<volatile int*>(s_abort), p.dev_status,
+                    DEV_TIMEOUT_PEER, LH_WAIT_TIMEOUT_NS);
   __syncthreads();
   return *reinterpret_cast<volatile int*>(s_abort) == 0;
 }

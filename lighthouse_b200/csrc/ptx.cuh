@@ -25,6 +25,8 @@ enum DeviceError : int {
   DEV_TIMEOUT_EPILOGUE = 103,
   DEV_TIMEOUT_SOFTMAX = 104,
   DEV_TIMEOUT_CORRECTION = 105,
+  DEV_TIMEOUT_PEER = 106,      // a flag another rank writes did not arrive
+  DEV_TIMEOUT_SELFTEST = 107,  // the wait the self-test lets run out on purpose
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -80,8 +82,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait. `abort_flag` lives in shared memory and is raised by whichever
 // role times out first so the other roles leave their loops quickly.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* dev_status, int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                int* dev_status, int code, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
@@ -89,13 +91,42 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
     if (((++spins) & 0xffu) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > LH_WAIT_TIMEOUT_NS) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         if (dev_status) atomicCAS(dev_status, 0, code);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* dev_status, int code) {
+  return mbar_wait_limit(bar, parity, abort_flag, dev_status, code, LH_WAIT_TIMEOUT_NS);
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded poll of a 32-bit flag in global memory (this GPU's or a peer's) until it has
+// reached `target`, compared as a signed distance so that a wrap of the counter is harmless.
+// Same give-up protocol as mbar_wait_limit.
+__device__ __forceinline__ bool flag_wait_limit(const uint32_t* flag, uint32_t target, volatile int* abort_flag,
+                                                int* dev_status, int code, uint64_t limit_ns) {
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(ld_acquire_sys_u32(flag) - target) < 0) {
+    if (((++spins) & 0x3fu) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > limit_ns) {
+        *abort_flag = 1;
+        if (dev_status) atomicCAS(dev_status, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
 }
 
 // ---------------------------------------------------------------------- TMA

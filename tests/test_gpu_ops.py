@@ -326,6 +326,28 @@ def test_launch_counter_and_status_word(ctx):
     assert ctx.launch_count == before + 1 and float(t.sum()) == 64.0
 
 
+def test_bounded_wait_gives_up_and_the_context_survives(own_stream_ctx):
+    """The give-up path of the device-side waits, exercised in its harmless form: waits on an
+    mbarrier and on a local flag that nothing will ever satisfy, with a 1 ms limit. The kernel
+    returns by itself, the next sync reports a device error once, and the same context then
+    runs a GEMM correctly."""
+    c = own_stream_ctx
+    assert c.selftest_bounded_wait(1_000_000) == 64
+    with pytest.raises(N.LighthouseCudaError, match="bounded wait"):
+        c.sync()
+    c.sync()  # the status word was cleared: no second report
+    a, b, _ = I.gemm_bf16_normal(128, 128, 64, seed=3)
+    a, b = a * 25, b * 25
+    ad, bd = dev(a), dev(b)
+    d = torch.empty(128, 128, device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    c.gemm(d, ad, bd)
+    c.sync()
+    assert_parity(host(d), R.gemm_epilogue(I.to_np(a), I.to_np(b), out_dtype="bf16"), "bf16")
+    with pytest.raises(ValueError):
+        c.selftest_bounded_wait(10**12)  # limits beyond 100 ms are refused
+
+
 def test_own_stream_mode_with_explicit_synchronisation(own_stream_ctx):
     """A context on its own non-blocking stream is ordered with torch by synchronising: torch's
     stream before the call (operands and the result buffer's fill are complete), the
