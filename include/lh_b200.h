@@ -269,9 +269,13 @@ int lh_b200_allgather(lh_ctx_t* ctx, const lh_memref_t* out, const lh_memref_t* 
  * whose loads can return the sum over all ranks' copies and whose stores reach all of them).
  * The host allocates and exchanges them (torch.distributed._symmetric_memory in this
  * repository's workloads) and registers the raw addresses here; the library never maps peer
- * memory itself. `pads` are the ranks' flag pads (>= 2 * LH_MAX_RANKS * 4 bytes each, zeroed
- * before the first use) through which the kernels order themselves across ranks; every wait
- * on them is bounded and ends in LH_ERR_DEVICE at the next lh_b200_sync.
+ * memory itself. `pads` are the ranks' flag pads (>= 2 * LH_MAX_RANKS * 4 bytes each) through
+ * which the kernels order themselves across ranks; lh_b200_symm_set_flags zeroes this rank's
+ * own pad and restarts the launch numbering, so all ranks call it together and pass a barrier
+ * before the first fused launch. Every wait on the pads is bounded and ends in LH_ERR_DEVICE at
+ * the next lh_b200_sync; after that (or after a failed launch of a fused kernel on any rank)
+ * the ranks' launch numbers may differ, further fused calls on that context are refused, and
+ * the flags have to be set up again on every rank.
  */
 #define LH_MAX_RANKS 8
 int lh_b200_symm_register(lh_ctx_t* ctx, void* local, size_t bytes, void* multicast, void* const* peers, int world);

@@ -57,17 +57,25 @@ int encode_tensor_map(lh_ctx* ctx, CUtensorMap* out, int dtype, int rank, void* 
   return LH_OK;
 }
 
+// Grows the context's scratch buffer. A buffer that is too small is not freed here - kernels
+// already queued may still use it, and freeing would need a device-wide wait in the middle of
+// a plan - but retired until the next lh_b200_sync, where the stream is idle anyway. Modules
+// size the scratch once at creation (module_scratch_bytes), so a plan never grows it mid-run.
+// The generation number lets a captured CUDA graph notice that the pointer it baked in is stale.
 int ensure_scratch(lh_ctx* ctx, size_t bytes) {
   if (ctx->scratch_bytes >= bytes) return LH_OK;
-  if (ctx->scratch) {
-    LH_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
-    LH_CUDA_CHECK(ctx, cudaFree(ctx->scratch));
-    ctx->scratch = nullptr;
-    ctx->scratch_bytes = 0;
-  }
-  LH_CUDA_CHECK(ctx, cudaMalloc(&ctx->scratch, bytes));
+  void* fresh = nullptr;
+  LH_CUDA_CHECK(ctx, cudaMalloc(&fresh, bytes));
+  if (ctx->scratch) ctx->retired_scratch.push_back(ctx->scratch);
+  ctx->scratch = fresh;
   ctx->scratch_bytes = bytes;
+  ctx->scratch_generation++;
   return LH_OK;
+}
+
+static void free_retired_scratch(lh_ctx* ctx) {
+  for (void* ptr : ctx->retired_scratch) cudaFree(ptr);
+  ctx->retired_scratch.clear();
 }
 
 // Unfused attention for what the tensor-core kernel does not take (f32 operands,
@@ -200,8 +208,10 @@ extern "C" int lh_b200_ctx_destroy(lh_ctx_t* ctx) {
   for (cudaEvent_t e : ctx->events)
     if (e) cudaEventDestroy(e);
   if (ctx->scratch) cudaFree(ctx->scratch);
+  for (void* ptr : ctx->retired_scratch) cudaFree(ptr);
   if (ctx->symm_counter) cudaFree(ctx->symm_counter);
   for (auto& t : ctx->rope_tables) cudaFree(t.data);
+  if (ctx->rope_built) cudaEventDestroy(ctx->rope_built);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
   if (ctx->host_status) cudaFreeHost(ctx->host_status);
   delete ctx;
@@ -223,8 +233,10 @@ extern "C" int lh_b200_sync(lh_ctx_t* ctx) {
   if (ctx->side_stream) LH_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->side_stream));
   LH_CUDA_CHECK(ctx, cudaMemcpyAsync(ctx->host_status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
   LH_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+  lh::free_retired_scratch(ctx);  // both streams are idle: nothing can still use an outgrown scratch buffer
   const int st = *ctx->host_status;
   if (st != 0) {
+    if (st == 106) ctx->symm_broken = true;  // a peer's flag never came: the ranks are out of step until the flags are set up again
     cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream);
     cudaStreamSynchronize(ctx->stream);
     return set_error(ctx, LH_ERR_DEVICE, "a kernel gave up on a bounded wait (device status %d)", st);
@@ -634,6 +646,28 @@ extern "C" int lh_b200_allgather(lh_ctx_t* ctx, const lh_memref_t* out, const lh
 }
 
 // ------------------------------------------------------------------- modules
+namespace lh {
+// Upper bound of the context scratch an operator can ask for, from its operand views alone
+// (the choice between kernels also looks at pointer alignment, which is not known yet).
+size_t op_scratch_bytes(const lh_op_t& op) {
+  if (op.kind == LH_OP_ATTENTION) {
+    const lh_view_t& q = op.operands[1];
+    const lh_view_t& k = op.operands[2];
+    if (q.slot < 0 || k.slot < 0 || q.rank < 3) return 0;
+    const int64_t d = q.shape[q.rank - 1];
+    if (q.dtype == LH_BF16 && (d == 64 || d == 128)) return 0;  // tensor-core kernel: no score matrix
+    return static_cast<size_t>(q.shape[q.rank - 2]) * static_cast<size_t>(k.shape[k.rank - 2]) * sizeof(float);
+  }
+  if (op.kind == LH_OP_GEMM) {
+    const lh_view_t& a = op.operands[1];
+    const lh_view_t& b = op.operands[2];
+    if (a.slot < 0 || b.slot < 0 || a.rank != 2 || a.dtype != LH_F32 || b.dtype != LH_F32) return 0;
+    return gemm_tc_tf32x3_scratch_bytes(static_cast<int>(a.shape[0]), static_cast<int>(b.shape[1]), static_cast<int>(a.shape[1]));
+  }
+  return 0;
+}
+}  // namespace lh
+
 struct lh_module {
   lh_ctx* ctx = nullptr;
   std::string entry;
@@ -644,6 +678,7 @@ struct lh_module {
   bool use_graph = false;
   cudaGraphExec_t graph_exec = nullptr;
   std::vector<void*> graph_args;
+  uint64_t graph_scratch_generation = 0;  // ctx->scratch_generation the graph was captured under
   // per-operator timing: one event before the first operator and one after each
   bool profiling = false;
   std::vector<cudaEvent_t> op_events;
@@ -662,6 +697,18 @@ extern "C" int lh_b200_module_create(lh_ctx_t* ctx, const char* entry_name, cons
       const lh_view_t& v = ops[i].operands[j];
       if (v.slot >= nslots) return set_error(ctx, LH_ERR_INVALID, "module_create: op %d operand %d names slot %d of %d", i, j, v.slot, nslots);
       if (v.slot >= 0 && (v.rank < 0 || v.rank > LH_MAX_RANK)) return set_error(ctx, LH_ERR_INVALID, "module_create: op %d operand %d has rank %d", i, j, v.rank);
+    }
+  }
+  // scratch the operators will ask for, allocated now instead of in the middle of a run
+  {
+    size_t need = 0;
+    for (int i = 0; i < nops; ++i) {
+      const size_t b = lh::op_scratch_bytes(ops[i]);
+      if (b > need) need = b;
+    }
+    if (need) {
+      int rc = ensure_scratch(ctx, need);
+      if (rc) return rc;
     }
   }
   lh_module* m = new lh_module();
@@ -761,7 +808,8 @@ extern "C" int lh_b200_module_run(lh_module_t* m, void* const* arg_ptrs, int nar
   if (nargs != static_cast<int>(m->args.size()) || (nargs && !arg_ptrs))
     return set_error(ctx, LH_ERR_INVALID, "module '%s' takes %zu arguments, got %d", m->entry.c_str(), m->args.size(), nargs);
   if (!m->use_graph) return run_ops(m, arg_ptrs);
-  bool same = m->graph_exec && m->graph_args.size() == static_cast<size_t>(nargs);
+  // a captured graph holds raw pointers: the arguments' and the context scratch's
+  bool same = m->graph_exec && m->graph_args.size() == static_cast<size_t>(nargs) && m->graph_scratch_generation == ctx->scratch_generation;
   for (int i = 0; same && i < nargs; ++i) same = (m->graph_args[i] == arg_ptrs[i]);
   if (!same) {
     if (m->graph_exec) {
@@ -785,6 +833,7 @@ extern "C" int lh_b200_module_run(lh_module_t* m, void* const* arg_ptrs, int nar
     cudaGraphDestroy(graph);
     LH_CUDA_CHECK(ctx, e);
     m->graph_args.assign(arg_ptrs, arg_ptrs + nargs);
+    m->graph_scratch_generation = ctx->scratch_generation;
     return LH_OK;  // the eager run above already produced this call's results
   }
   LH_CUDA_CHECK(ctx, cudaGraphLaunch(m->graph_exec, ctx->stream));
@@ -829,8 +878,13 @@ extern "C" int lh_b200_module_op_end_times(lh_module_t* m, float* ms, int n) {
 extern "C" int lh_b200_module_use_graph(lh_module_t* m, int enable) {
   if (!m) return LH_ERR_INVALID;
   if (enable)
-    for (const lh_op_t& op : m->ops)
+    for (const lh_op_t& op : m->ops) {
       if (op.kind == LH_OP_STREAM) return set_error(m->ctx, LH_ERR_UNSUPPORTED, "graph mode is not available for modules that use the side stream");
+      // the cross-rank kernel takes a launch number that every replay would repeat: its flag
+      // waits would pass at once from the second replay on and the ranks would run unordered
+      if (op.kind == LH_OP_REDUCE_NORM_GATHER && m->ctx->symm_world > 1)
+        return set_error(m->ctx, LH_ERR_UNSUPPORTED, "graph mode is not available for modules with the multi-rank reduce_norm_gather operator");
+    }
   m->use_graph = enable != 0;
   return LH_OK;
 }

@@ -40,7 +40,14 @@ struct Attn3Params {
   int causal;
   int num_q_pairs;
   int* dev_status;
+  long long* dbg;  // development only: timeline of one block
+  int dbg_block;
 };
+
+#define DBG_MARK(j, slot)                                                                      \
+  do {                                                                                         \
+    if (p.dbg && blockIdx.x == p.dbg_block && (j) < 12) p.dbg[(j) * 16 + (slot)] = clock64();   \
+  } while (0)
 
 template <int HD>
 struct Attn3Smem {
@@ -79,7 +86,10 @@ __device__ __forceinline__ int kv_tiles_for(const Attn3Params& p, int q0) {
   return n;
 }
 
-template <int HD>
+// TV: timing experiments (development only). bit 0: no row-max pass (wrong results unless the
+// scores are small); bit 1: no exponentials (wrong results); bit 2: one pass over the scores
+// with the whole row in registers (correct).
+template <int HD, int TV>
 __global__ void __launch_bounds__(ATT3_THREADS, 1)
 attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const Attn3Params p) {
@@ -177,7 +187,93 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    if (TV & 16) {
+      // The whole warp walks the schedule (waits included) and one elected lane issues: all
+      // descriptor arithmetic stays warp-uniform, and per MMA it is one 64-bit add of a
+      // compile-time constant to a descriptor built once per product.
+      constexpr uint32_t idesc_qk = make_idesc(UMMA_BF16, BQ3, BKV3, false, false);
+      constexpr uint32_t idesc_pv = make_idesc(UMMA_BF16, BQ3, HD, false, true);
+      const uint32_t q_addr = smem_u32(smem + L::Q_OFF);
+      const uint32_t k_addr = smem_u32(smem + L::K_OFF);
+      const uint32_t v_addr = smem_u32(smem + L::V_OFF);
+      auto issue_qk = [&](int t, int j) {
+        const uint64_t qd = make_smem_desc_sw128(q_addr + t * L::Q_BYTES, 16, 1024);
+        const uint64_t kd = make_smem_desc_sw128(k_addr + (j & 1) * L::KV_BYTES, 16, 1024);
+        const uint32_t d = tmem_base + S_COL + t * 128;
+        if (elect_one()) {
+#pragma unroll
+          for (int k = 0; k < HD / 16; ++k) {
+            constexpr int dummy = 0;
+            (void)dummy;
+            const uint64_t off = static_cast<uint64_t>(((k / 4) * SUBTILE3 + (k % 4) * 32) >> 4);  // address field counts 16-byte units
+            umma_f16_ss(d, qd + off, kd + off, idesc_qk, k != 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[t]);
+        }
+        __syncwarp();
+      };
+      bool ok = wait_warp3(q_full, 0, abort_flag, p.dev_status, DEV_TIMEOUT_MMA);
+      if (ok && n_max > 0) {
+        ok = wait_warp3(&k_full[0], 0, abort_flag, p.dev_status, DEV_TIMEOUT_MMA);
+        if (ok) {
+          tc_fence_after_sync();
+          for (int t = 0; t < 2; ++t)
+            if (n_of(t) > 0) issue_qk(t, 0);
+          if (elect_one()) umma_commit(&k_empty[0]);
+          __syncwarp();
+        }
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1u;
+        const uint32_t tph = j & 1u;
+        const bool have_next = j + 1 < n_max;
+        if (!wait_warp3(&v_full[st], ph, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) break;
+        bool next_k_seen = false;
+        const uint64_t vd = make_smem_desc_sw128(v_addr + st * L::KV_BYTES, SUBTILE3, 1024);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j < n_of(t)) {
+            if (lane == 0) DBG_MARK(j, t * 4 + 0);
+            const uint32_t od = tmem_base + O_COL + t * 128, pa = tmem_base + S_COL + t * 128;
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              if (!wait_warp3(&p_half[2 * t + hf], tph, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+              if (elect_one()) {
+#pragma unroll
+                for (int k = hf * 4; k < hf * 4 + 4; ++k)
+                  umma_f16_ts(od, pa + k * 8, vd + static_cast<uint64_t>((k * 2048) >> 4), idesc_pv, (j | k) != 0 ? 1u : 0u);
+                if (hf == 1) umma_commit(&pv_done[t]);
+              }
+              __syncwarp();
+            }
+            if (!ok) break;
+            if (lane == 0) DBG_MARK(j, t * 4 + 1);
+          }
+          if (j + 1 < n_of(t)) {
+            if (!next_k_seen) {
+              if (!wait_warp3(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+              next_k_seen = true;
+            }
+            issue_qk(t, j + 1);
+            if (lane == 0) DBG_MARK(j, t * 4 + 2);
+          }
+        }
+        if (!ok) break;
+        if (elect_one()) {
+          umma_commit(&v_empty[st]);
+          if (have_next) umma_commit(&k_empty[(j + 1) & 1]);
+        }
+        __syncwarp();
+      }
+    } else if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(UMMA_BF16, BQ3, BKV3, false, false);
       constexpr uint32_t idesc_pv = make_idesc(UMMA_BF16, BQ3, HD, false, true);
       const uint32_t q_addr = smem_u32(smem + L::Q_OFF);
@@ -216,6 +312,7 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             // O_t += P_t V_j, P_t read from tensor memory, its first 64 keys consumed while the
             // softmax warps still produce the rest
             const uint32_t va = v_addr + st * L::KV_BYTES;
+            DBG_MARK(j, t * 4 + 0);
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
               if (!mbar_wait(&p_half[2 * t + hf], tph, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
@@ -232,6 +329,7 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
             if (!ok) break;
             umma_commit(&pv_done[t]);
+            DBG_MARK(j, t * 4 + 1);
           }
           if (j + 1 < n_of(t)) {
             // The next scores of this tile overwrite the columns the product just issued reads P
@@ -245,6 +343,7 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               next_k_seen = true;
             }
             issue_qk(t, j + 1);
+            DBG_MARK(j, t * 4 + 2);
           }
         }
         if (!ok) break;
@@ -274,11 +373,32 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         break;
       }
       tc_fence_after_sync();
+      if (row == 0) DBG_MARK(j, 8 + t * 4 + 0);
       const int col0 = j * BKV3;
       const bool need_mask = (col0 + BKV3 > p.Skv) || (p.causal && (col0 + BKV3 - 1 > q0t + offset));
       const int limit = need_mask ? (p.causal ? min(p.Skv - 1, q_row + offset) : (p.Skv - 1)) - col0 : BKV3;  // last visible column in this tile
       // pass 1: row max of the scores, two 32-column loads in flight at a time
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;  // independent chains
+      uint32_t sr[(TV & 4) ? 128 : 1];  // TV bit 2: the whole row of scores
+      if (TV & 4) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[(TV & 4) ? c * 32 : 0]));
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < ((TV & 4) ? 128 : 1); ++i)
+            if (i > limit) sr[i] = 0xff800000u;
+        }
+#pragma unroll
+        for (int i = 0; i < ((TV & 4) ? 128 : 1); i += 8) {
+          mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+          mx2 = fmax3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+          mx3 = fmax3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
+        }
+      } else if (TV & 1) {
+        mx0 = 0.f;
+      } else
 #pragma unroll
       for (int c = 0; c < 4; c += 2) {
         uint32_t s0[32], s1[32];
@@ -300,6 +420,7 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mx3 = fmax3(mx3, __uint_as_float(s1[i + 2]), __uint_as_float(s1[i + 3]));
         }
       }
+      if (row == 0) DBG_MARK(j, 8 + t * 4 + 1);
       float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       mx *= p.scale_log2;  // scale > 0: max commutes with the scaling
       // lazy rescale: move the reference max only when it grew by more than 8 (2^8 headroom)
@@ -329,17 +450,27 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
-        uint32_t s0[32], s1[32];
-        tmem_ld_32x32b_x32(s_addr + hf * 64, s0);
-        tmem_ld_32x32b_x32(s_addr + hf * 64 + 32, s1);
-        tmem_ld_wait();
+        uint32_t s0l[(TV & 4) ? 1 : 32], s1l[(TV & 4) ? 1 : 32];
+        if (!(TV & 4)) {
+          tmem_ld_32x32b_x32(s_addr + hf * 64, *reinterpret_cast<uint32_t(*)[32]>(&s0l[0]));
+          tmem_ld_32x32b_x32(s_addr + hf * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&s1l[0]));
+          tmem_ld_wait();
+        }
+        const uint32_t* s0 = (TV & 4) ? &sr[(TV & 4) ? hf * 64 : 0] : s0l;
+        const uint32_t* s1 = (TV & 4) ? &sr[(TV & 4) ? hf * 64 + 32 : 0] : s1l;
         uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(s0[2 * i]), p.scale_log2, -msub));
-          float p1 = ex2_approx(fmaf(__uint_as_float(s0[2 * i + 1]), p.scale_log2, -msub));
-          float p2 = ex2_approx(fmaf(__uint_as_float(s1[2 * i]), p.scale_log2, -msub));
-          float p3 = ex2_approx(fmaf(__uint_as_float(s1[2 * i + 1]), p.scale_log2, -msub));
+          float p0 = fmaf(__uint_as_float(s0[2 * i]), p.scale_log2, -msub);
+          float p1 = fmaf(__uint_as_float(s0[2 * i + 1]), p.scale_log2, -msub);
+          float p2 = fmaf(__uint_as_float(s1[2 * i]), p.scale_log2, -msub);
+          float p3 = fmaf(__uint_as_float(s1[2 * i + 1]), p.scale_log2, -msub);
+          if (!(TV & 2)) {
+            p0 = ex2_approx(p0);
+            p1 = ex2_approx(p1);
+            p2 = ex2_approx(p2);
+            p3 = ex2_approx(p3);
+          }
           if (need_mask) {
             const int cbase = hf * 64 + 2 * i;
             p0 = (cbase <= limit) ? p0 : 0.f;
@@ -358,6 +489,7 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_st_wait();
         tc_fence_before_sync();
         mbar_arrive(&my_p_half[hf]);
+        if (row == 0) DBG_MARK(j, 8 + t * 4 + 2 + hf);
       }
       l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
     }
@@ -398,7 +530,7 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 }
 
-template <int HD>
+template <int HD, int TV>
 int launch3_hd(lh_ctx* ctx, const AttnProblem& a) {
   using L = Attn3Smem<HD>;
   CUtensorMap tmQ, tmK, tmV;
@@ -425,11 +557,38 @@ int launch3_hd(lh_ctx* ctx, const AttnProblem& a) {
   p.causal = a.causal;
   p.num_q_pairs = (a.Sq + 2 * BQ3 - 1) / (2 * BQ3);
   p.dev_status = ctx->dev_status;
-  auto kernel = attn_fwd_tc3_kernel<HD>;
+  p.dbg = nullptr;
+  p.dbg_block = 0;
+  static const int dbg_on = getenv("LH_ATTN_DBG") ? atoi(getenv("LH_ATTN_DBG")) : -1;
+  static long long* dbg_buf = nullptr;
+  if (dbg_on >= 0) {
+    if (!dbg_buf) cudaMalloc(&dbg_buf, 12 * 16 * sizeof(long long));
+    cudaMemsetAsync(dbg_buf, 0, 12 * 16 * sizeof(long long), ctx->stream);
+    p.dbg = dbg_buf;
+    p.dbg_block = dbg_on;
+  }
+  auto kernel = attn_fwd_tc3_kernel<HD, TV>;
   LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   const int64_t grid = static_cast<int64_t>(a.B) * a.Hq * p.num_q_pairs;
   kernel<<<static_cast<unsigned>(grid), ATT3_THREADS, L::DYN_BYTES, ctx->stream>>>(tmQ, tmK, tmV, p);
   LH_CHECK_LAUNCH(ctx, "attn_fwd_tc3_kernel");
+  if (dbg_on >= 0) {
+    static int printed = 0;
+    long long h[12 * 16];
+    cudaStreamSynchronize(ctx->stream);
+    cudaMemcpy(h, dbg_buf, sizeof(h), cudaMemcpyDeviceToHost);
+    if (printed++ == 3) {
+      long long t0 = 0;
+      for (int i = 0; i < 12 * 16; ++i)
+        if (h[i] && (!t0 || h[i] < t0)) t0 = h[i];
+      fprintf(stderr, "attn timeline (clk from first mark): per j: MMA A[pv_wait pv_issued qk_issued -] B[...] | softmax A[s_full pass1 half0 half1] B[...]\n");
+      for (int j = 0; j < 12; ++j) {
+        fprintf(stderr, "j=%2d:", j);
+        for (int k = 0; k < 16; ++k) fprintf(stderr, " %6lld%s", h[j * 16 + k] ? h[j * 16 + k] - t0 : -1, (k % 4 == 3) ? " |" : "");
+        fprintf(stderr, "\n");
+      }
+    }
+  }
   return LH_OK;
 }
 
@@ -437,8 +596,20 @@ int launch3_hd(lh_ctx* ctx, const AttnProblem& a) {
 
 int attn_tc3_launch(lh_ctx* ctx, const AttnProblem& a) {
   if (a.scale <= 0.f) return set_error(ctx, LH_ERR_UNSUPPORTED, "attention: scale must be positive");
-  if (a.D == 128) return launch3_hd<128>(ctx, a);
-  return launch3_hd<64>(ctx, a);
+  static const int tv = getenv("LH_ATTN_TEST") ? atoi(getenv("LH_ATTN_TEST")) : 0;  // experiment switch (development only)
+  if (a.D == 128) {
+    switch (tv) {
+      case 1: return launch3_hd<128, 1>(ctx, a);
+      case 2: return launch3_hd<128, 2>(ctx, a);
+      case 3: return launch3_hd<128, 3>(ctx, a);
+      case 4: return launch3_hd<128, 4>(ctx, a);
+      case 6: return launch3_hd<128, 6>(ctx, a);
+      case 16: return launch3_hd<128, 16>(ctx, a);
+      case 19: return launch3_hd<128, 19>(ctx, a);
+      default: return launch3_hd<128, 0>(ctx, a);
+    }
+  }
+  return launch3_hd<64, 0>(ctx, a);
 }
 
 // What the tensor-core kernels take: bf16 Q / K / V with unit stride in the head dimension,

@@ -40,6 +40,8 @@ struct lh_ctx {
   // scratch for split/partial results and for L2 flushing in benchmarks
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
+  uint64_t scratch_generation = 0;        // bumped whenever `scratch` is replaced
+  std::vector<void*> retired_scratch;     // outgrown buffers, freed at the next lh_b200_sync
   // NCCL
   void* nccl_lib = nullptr;
   void* nccl_comm = nullptr;
@@ -55,10 +57,12 @@ struct lh_ctx {
   uint32_t* symm_pads[LH_MAX_RANKS] = {nullptr};  // every rank's flag pad as mapped here
   int symm_rank = 0, symm_world = 0;
   uint32_t symm_epoch = 0;            // launches of flag-synchronised kernels so far (same on every rank)
+  bool symm_broken = false;           // a fused launch failed here: launch numbers may differ between ranks
   uint32_t* symm_counter = nullptr;   // device word: blocks finished in the running launch
   // rotary tables built so far
-  struct RopeTable { float theta; int pos0, seq, dim; float* data; };
+  struct RopeTable { float theta; int dim, positions; float* data; };  // (cos, sin) of positions [0, positions)
   std::vector<RopeTable> rope_tables;
+  cudaEvent_t rope_built = nullptr;   // orders a table's build before the other stream's later work
 };
 
 namespace lh {
@@ -146,6 +150,7 @@ int gemm_tc_bf16_supported(const lh_ctx* ctx, const GemmProblem& p);
 int gemm_tc_bf16_launch(lh_ctx* ctx, const GemmProblem& p);
 int gemm_tc_tf32x3_supported(const lh_ctx* ctx, const GemmProblem& p);
 int gemm_tc_tf32x3_launch(lh_ctx* ctx, const GemmProblem& p);
+size_t gemm_tc_tf32x3_scratch_bytes(int M, int N, int K);  // 0 where the 3xTF32 path does not apply
 int gemm_simt_launch(lh_ctx* ctx, const GemmProblem& p);
 
 // -------------------------------------------------------- attention problem

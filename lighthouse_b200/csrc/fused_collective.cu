@@ -240,6 +240,11 @@ extern "C" int lh_b200_symm_set_flags(lh_ctx_t* ctx, int rank, int world, void* 
   ctx->symm_rank = rank;
   ctx->symm_world = world;
   ctx->symm_epoch = 0;
+  ctx->symm_broken = false;
+  // The launch numbering restarts, so this rank's pad must read zero again. The caller runs a
+  // barrier over all ranks after this call and before the first fused launch: no rank may
+  // signal into a pad its owner has not cleared yet.
+  LH_CUDA_CHECK(ctx, cudaMemset(pads[rank], 0, 2 * LH_MAX_RANKS * sizeof(uint32_t)));
   if (!ctx->symm_counter) {
     LH_CUDA_CHECK(ctx, cudaMalloc(&ctx->symm_counter, sizeof(uint32_t)));
     LH_CUDA_CHECK(ctx, cudaMemset(ctx->symm_counter, 0, sizeof(uint32_t)));
@@ -315,16 +320,24 @@ extern "C" int lh_b200_reduce_norm_gather(lh_ctx_t* ctx, const lh_memref_t* xn, 
     if (!ctx->symm_pads[i]) return set_error(ctx, LH_ERR_INVALID, "reduce_norm_gather: flag pads not set");
     p.pads[i] = ctx->symm_pads[i];
   }
+  if (ctx->symm_broken)
+    return set_error(ctx, LH_ERR_DEVICE, "reduce_norm_gather: a launch on this context failed, so the ranks' launch numbers may have parted; set the flags up again (lh_b200_symm_set_flags on every rank)");
   p.counter = ctx->symm_counter;
-  p.epoch = ++ctx->symm_epoch;
+  p.epoch = ctx->symm_epoch + 1;  // counted only once the launch is known to have gone out
   // The kernel shares the GPU with a persistent GEMM on the main stream: stay within the
   // SMs that GEMM leaves free, so that no block waits for an SM behind it.
   // (one block per SM; alone on the GPU the kernel takes all of it).
-  unsigned cap = static_cast<unsigned>(ctx->reserved_sms > 0 ? ctx->reserved_sms : ctx->sm_count);
-  const char* env = getenv("LH_B200_RNG_BLOCKS");
-  if (env && atoi(env) > 0) cap = static_cast<unsigned>(atoi(env));
+  const unsigned cap = static_cast<unsigned>(ctx->reserved_sms > 0 ? ctx->reserved_sms : ctx->sm_count);
   const unsigned grid = want < cap ? want : cap;
   reduce_norm_gather_kernel<true><<<grid, RNG_THREADS, RNG_SMEM_FENCE, ctx->stream>>>(p);
-  LH_CHECK_LAUNCH(ctx, "reduce_norm_gather_kernel");
+  {
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      ctx->symm_broken = true;  // the other ranks launched and this one did not
+      return set_error(ctx, LH_ERR_CUDA, "launch of reduce_norm_gather_kernel failed: %s", cudaGetErrorString(e));
+    }
+  }
+  ctx->launches++;
+  ctx->symm_epoch++;
   return LH_OK;
 }

@@ -508,11 +508,6 @@ int pick_bn(const lh_ctx* ctx, const GemmProblem& p) {
   if (p.flags & LH_GEMM_SWIGLU) return 256;
   const int hint = static_cast<int>((p.flags >> 8) & 0xffu) * 8;  // the caller's tile database
   if (hint == 64 || hint == 128 || hint == 192 || hint == 256) return hint;
-  const char* env = getenv("LH_B200_GEMM_BN");  // tuning override, read per call
-  if (env) {
-    const int v = atoi(env);
-    if (v == 64 || v == 128 || v == 192 || v == 256) return v;
-  }
   // Cost model: waves of tiles over the SMs times the per-tile time; narrower tiles
   // re-read A more often per flop, which the relative efficiencies account for.
   const int cand[3] = {256, 192, 128};
@@ -660,6 +655,13 @@ int gemm_tc_tf32x3_supported(const lh_ctx* ctx, const GemmProblem& p) {
   if (p.R && (p.r_dtype != LH_F32 || p.srn != 1 || (p.srm % 4) != 0 || !aligned16(p.R))) return 0;
   if (p.bias && ((p.bias_dtype != LH_BF16 && p.bias_dtype != LH_F32) || !aligned16(p.bias))) return 0;
   return 1;
+}
+
+size_t gemm_tc_tf32x3_scratch_bytes(int M, int N, int K) {
+  if (M < 1 || K < 1 || N < 8 || N % 8 || static_cast<int64_t>(M) * N * K < TF32X3_MIN_WORK) return 0;
+  const size_t a_bytes = static_cast<size_t>(M) * tf32x3_ld(K) * 4, b_bytes = static_cast<size_t>(N) * tf32x3_ld(K) * 4;
+  const size_t total = ((a_bytes + 255) & ~static_cast<size_t>(255)) + b_bytes;
+  return total > TF32X3_MAX_SCRATCH ? 0 : total;
 }
 
 int gemm_tc_tf32x3_launch(lh_ctx* ctx, const GemmProblem& p) {

@@ -487,21 +487,45 @@ int rope_launch(lh_ctx* ctx, const lh_memref_t* x, float theta, int pos0) {
   return LH_OK;
 }
 
+// One table per (theta, head size), covering positions [0, positions): a call for positions
+// [pos0, pos0 + seq) indexes into it, so a decode loop with a moving pos0 neither allocates nor
+// rebuilds. A table that is too short is replaced by one at least twice as long; the old one
+// is retired with the outgrown scratch buffers (freed at the next lh_b200_sync, and captured
+// graphs see the generation change). The build is ordered before later work of BOTH streams.
 int rope_table_for(lh_ctx* ctx, float theta, int pos0, int seq, int dim, const float** table) {
-  for (const auto& t : ctx->rope_tables)
-    if (t.theta == theta && t.pos0 == pos0 && t.seq == seq && t.dim == dim) {
-      *table = t.data;
-      return LH_OK;
-    }
-  if (seq < 1 || dim < 2 || dim % 2) return set_error(ctx, LH_ERR_INVALID, "rope table: seq %d, head size %d", seq, dim);
+  if (seq < 1 || dim < 2 || dim % 2 || pos0 < 0) return set_error(ctx, LH_ERR_INVALID, "rope table: positions %d + %d, head size %d", pos0, seq, dim);
+  const int need = pos0 + seq;
+  lh_ctx::RopeTable* slot = nullptr;
+  for (auto& t : ctx->rope_tables)
+    if (t.theta == theta && t.dim == dim) slot = &t;
+  if (slot && slot->positions >= need) {
+    *table = slot->data + static_cast<size_t>(pos0) * dim;  // (cos, sin) pairs: dim floats per position
+    return LH_OK;
+  }
+  int positions = 256;
+  while (positions < need) positions *= 2;
+  if (slot && positions < 2 * slot->positions) positions = 2 * slot->positions;
   void* mem = nullptr;
-  const int n = seq * (dim / 2);
+  const int64_t n = static_cast<int64_t>(positions) * (dim / 2);
   int rc = lh_b200_malloc(ctx, static_cast<size_t>(n) * sizeof(float2), &mem);
   if (rc) return rc;
-  rope_table_kernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>(static_cast<float2*>(mem), seq, dim, theta, pos0);
+  rope_table_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, ctx->stream>>>(static_cast<float2*>(mem), positions, dim, theta, 0);
   LH_CHECK_LAUNCH(ctx, "rope_table_kernel");
-  ctx->rope_tables.push_back({theta, pos0, seq, dim, static_cast<float*>(mem)});
-  *table = static_cast<float*>(mem);
+  cudaStream_t other = ctx->side_selected ? ctx->main_saved : ctx->side_stream;
+  if (other) {
+    if (!ctx->rope_built) LH_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->rope_built, cudaEventDisableTiming));
+    LH_CUDA_CHECK(ctx, cudaEventRecord(ctx->rope_built, ctx->stream));
+    LH_CUDA_CHECK(ctx, cudaStreamWaitEvent(other, ctx->rope_built, 0));
+  }
+  if (slot) {
+    ctx->retired_scratch.push_back(slot->data);
+    ctx->scratch_generation++;
+    slot->data = static_cast<float*>(mem);
+    slot->positions = positions;
+  } else {
+    ctx->rope_tables.push_back({theta, dim, positions, static_cast<float*>(mem)});
+  }
+  *table = static_cast<float*>(mem) + static_cast<size_t>(pos0) * dim;
   return LH_OK;
 }
 

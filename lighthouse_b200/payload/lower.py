@@ -544,6 +544,38 @@ def _widening_copy_source(plan: Plan, v: PView, reader: PlanOp):
     return w, w.operands[1]
 
 
+def _fold_inplace_consumer(plan: Plan, i: int, g, d) -> bool:
+    """The op right after a GEMM updates the GEMM's result in place (``outs`` used as an input,
+    the form of the reference's own exemplar, test/opt/pipeline-check.mlir:21-47: matmul,
+    bias add and ReLU as three generics over one tensor): fold it into the GEMM's epilogue.
+    Nothing is retargeted, so it does not matter which buffer D is or who reads it later."""
+    if i + 1 >= len(plan.ops):
+        return False
+    nxt = plan.ops[i + 1]
+    if nxt.kind != "elementwise" or nxt.operands[0] is None or nxt.operands[0] != d:
+        return False
+    out, a, b = nxt.operands[:3]
+    ew, act = nxt.attrs["ew"], nxt.attrs.get("act", "none")
+    has_bias, has_act, has_res = g.operands[4] is not None, g.attrs.get("act", "none") != "none", g.operands[5] is not None
+    reads_d = [v for v in (a, b) if v is not None and v == d]
+    if len(reads_d) != 1:
+        return False
+    other = b if a == d else a
+    n = d.shape[-1]
+    if ew == "act" and act == "relu" and not has_act and not has_res:
+        g.attrs["act"] = "relu"
+    elif ew in ("add", "add_act") and other is not None and _is_row_vector_bcast(other, n) and not has_bias and not has_act and not has_res and d.rank == 2:
+        g.operands[4] = PView(other.slot, (n,), (1,), other.dtype, other.offset)
+        if ew == "add_act":
+            g.attrs["act"] = act
+    elif ew == "add" and other is not None and other.shape == d.shape and other.slot != d.slot and not has_res and other.dtype == d.dtype:
+        g.operands[5] = other
+    else:
+        return False
+    del plan.ops[i + 1]
+    return True
+
+
 def fuse_gemm_epilogues(plan: Plan) -> int:
     """Folds bias add, cast, ReLU and residual add that consume a GEMM's output into that
     GEMM (the consumers ``get_tileable_consumers`` finds in the reference). The GEMM moves to
@@ -556,6 +588,10 @@ def fuse_gemm_epilogues(plan: Plan) -> int:
             if g.kind != "gemm" or g.attrs.get("flags", 0) & ~1:  # SwiGLU / forced-SIMT keep their epilogue
                 continue
             d = g.operands[0]
+            if _fold_inplace_consumer(plan, i, g, d):
+                fused += 1
+                changed = True
+                break
             if not _whole_temp(plan, d) or (g.operands[3] is not None and g.operands[3] == d):
                 continue
             writers, readers = _uses(plan, d.slot)

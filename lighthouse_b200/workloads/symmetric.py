@@ -57,12 +57,11 @@ class SymmetricBuffers:
 
         flags = symm_mem.empty(FLAG_PAD_WORDS, dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()))
         handle = self._rendezvous(flags)
-        flags.zero_()
+        offset = flags.data_ptr() - int(handle.buffer_ptrs[self.rank])
+        self.ctx.symm_set_flags(self.rank, self.world, [int(ptr) + offset for ptr in handle.buffer_ptrs])  # zeroes this rank's pad
         torch.cuda.synchronize()
         dist.barrier(group=self.group)  # every pad is zero before anyone's kernel signals
         torch.cuda.synchronize()
-        offset = flags.data_ptr() - int(handle.buffer_ptrs[self.rank])
-        self.ctx.symm_set_flags(self.rank, self.world, [int(ptr) + offset for ptr in handle.buffer_ptrs])
         self._flags_set = True
 
     def close(self):

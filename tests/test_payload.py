@@ -83,7 +83,11 @@ def test_generic_form_matmul_bias_relu_is_recognised():
     out = CpuPlanRunner(plan).run([a, b, bias, c])[3]
     want = np.maximum(a @ b + c + bias, 0.0)
     assert max_rel_err(out, want) < 1e-6
-    assert [op.kind for op in plan.ops].count("gemm") == 1
+    # the three in-place generics (the form of test/opt/pipeline-check.mlir:21-47 in the
+    # reference) become ONE operator: a GEMM accumulating into its output with bias and ReLU
+    # in its epilogue
+    assert [op.kind for op in plan.ops] == ["gemm"]
+    assert plan.ops[0].operands[4] is not None and plan.ops[0].attrs["act"] == "relu"
 
 
 def test_unsupported_payloads_raise_value_error():
