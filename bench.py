@@ -241,8 +241,15 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
         tp, dp = n, 1
     else:
         cfg = D.NanoGptConfig(n_layer=args.layers or 12)
-        tp = n if n <= 4 else 4  # 12 heads do not split 8 ways: 8 GPUs = TP4 x 2 batch halves
-        dp = n // tp
+        if args.nanogpt_layout == "dp":
+            # the 16 sequences are split over the ranks: a forward pass then needs no exchange at
+            # all (at d_model 768 the all-reduce of the f32 residual costs more than it saves)
+            if cfg.batch % n:
+                raise SystemExit(f"batch {cfg.batch} does not split over {n} GPUs")
+            tp, dp = 1, n
+        else:
+            tp = n if n <= 4 else 4  # 12 heads do not split 8 ways: 8 GPUs = TP4 x 2 batch halves
+            dp = n // tp
         cfg = D.NanoGptConfig(n_layer=cfg.n_layer, batch=cfg.batch // dp)
     D.check_tp(cfg, tp)
     tp_rank, group = dist.rank % tp, dist.rank // tp
@@ -387,7 +394,7 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {
             "workload": workload_description(args),
-            "parallelism": f"tp{tp}" + (f"xdp{dp}" if dp > 1 else "") + (f", {'fused multimem reduce+norm+gather kernel' if fused else 'NCCL reduce-scatter/all-gather'} of {args.microbatches} micro-batches overlapped with compute" if overlapped else ""), "tokens_per_step": total_tokens, "l2": "inputs_exceed_l2 (weights + activations >> 126 MB)",
+            "parallelism": (f"dp{dp}: {cfg.batch} of {cfg.batch * dp} sequences per GPU, no collective in the forward pass" if (tp == 1 and dp > 1) else f"tp{tp}" + (f"xdp{dp}" if dp > 1 else "")) + (f", {'fused multimem reduce+norm+gather kernel' if fused else 'NCCL reduce-scatter/all-gather'} of {args.microbatches} micro-batches overlapped with compute" if overlapped else ""), "tokens_per_step": total_tokens, "l2": "inputs_exceed_l2 (weights + activations >> 126 MB)",
             "algorithmic_tflop_per_step": round(flops / 1e12, 3),
         },
         "model_tflops": round(flops / step_s / 1e12, 1), "model_frac_of_peak": round(flops / step_s / 1e12 / (n * peaks["bf16_tflops_sustained"]), 4),
@@ -851,6 +858,7 @@ def main() -> int:
     ap.add_argument("--collectives", choices=["fused", "nccl"], default="fused", help="tensor parallel with micro-batches: one multimem kernel per reduce+norm+gather, or NCCL reduce-scatter / all-gather around row kernels")
     ap.add_argument("--timeline", default="", help="decoder workloads: write rank 0's per-operator timeline of the last timed step to this file")
     ap.add_argument("--reserve-sms", type=int, default=8, help="SMs the persistent GEMMs leave to the collectives in the overlapped schedule")
+    ap.add_argument("--nanogpt-layout", choices=["dp", "tp"], default="dp", help="nanoGPT on N GPUs: sequences split over the ranks (no collective), or tensor parallel (TP <= 4, 8 GPUs = TP4 x 2 batch halves)")
     ap.add_argument("--no-kernels", action="store_true", help="skip the GEMM / attention kernel lines of the decoder workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="decoder workloads: skip the full-depth check of the result against the CPU oracle")

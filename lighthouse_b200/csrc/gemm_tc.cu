@@ -29,7 +29,8 @@ constexpr int BM = 128;
 constexpr int BK = 64;                      // 64 bf16 = one 128-byte swizzle row
 constexpr int A_TILE_BYTES = BM * BK * 2;   // 16 KiB
 constexpr int NUM_THREADS = 192;
-constexpr int GROUP_M = 16;                 // tile rasterisation: 16 row-blocks share B column-blocks in L2
+constexpr int GROUP_M_MIN = 16;             // tile rasterisation: at least 16 row-blocks share B column-blocks in L2
+constexpr size_t GROUP_A_PANEL_BYTES = 36u << 20;  // how much of A a group may keep resident in L2
 constexpr int STAGING_BUF_BYTES = 32 * 128; // 32 rows x 128 bytes
 constexpr int STAGING_BYTES = 4 * 2 * STAGING_BUF_BYTES;  // 4 epilogue warps x 2 buffers
 
@@ -37,6 +38,7 @@ struct GemmTcParams {
   int M, N, K;
   int n_out;  // columns of D (N, or N/2 with the SwiGLU epilogue)
   int num_m_blocks, num_n_blocks, num_k_blocks;
+  int group_m;  // row-blocks per rasterisation group
   EpiParams epi;
   int* dev_status;
 };
@@ -57,11 +59,15 @@ struct SmemLayout {
   static_assert(DYN_BYTES <= 232448, "exceeds the 227 KiB of shared memory a CTA can opt into");
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
-  const int group_size = GROUP_M * num_n;
+// Tiles are walked group by group: a group is `group_m` row-blocks times all column-blocks,
+// row-blocks fastest. Within a group every A row-panel is fetched from HBM once and found in
+// L2 by the later column-blocks; B is streamed once per group, so the fewer groups the less
+// B traffic - as long as the group's A panel still fits in L2 beside the stream.
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int group_m, int& m_blk, int& n_blk) {
+  const int group_size = group_m * num_n;
   const int group = tile / group_size;
-  const int first_m = group * GROUP_M;
-  const int rows = min(num_m - first_m, GROUP_M);
+  const int first_m = group * group_m;
+  const int rows = min(num_m - first_m, group_m);
   const int in_group = tile - group * group_size;
   m_blk = first_m + in_group % rows;
   n_blk = in_group / rows;
@@ -211,7 +217,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(tile, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+        tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, m_blk, n_blk);
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -283,7 +289,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       int m_blk, n_blk;
-      tile_coords(tile, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+      tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, m_blk, n_blk);
       const int buf = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1u;
       if (!mbar_wait_warp(&tmem_full[buf], acc_phase, abort_flag, p.dev_status, DEV_TIMEOUT_EPILOGUE, lane))
@@ -480,6 +486,14 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi) {
   p.num_m_blocks = (pr.M + BM - 1) / BM;
   p.num_n_blocks = (pr.N + BN - 1) / BN;
   p.num_k_blocks = (pr.K + static_cast<int>(BKE) - 1) / static_cast<int>(BKE);
+  // Widest group whose A panel (group_m x 128 rows x K) stays within a quarter of L2: 64
+  // row-blocks up to K = 2048, 32 up to 4096, 16 beyond (measured at 16 with K = 4096,
+  // N = 28672: B read 8 times, 2.0 GB of DRAM reads for 0.37 GB of operands).
+  p.group_m = GROUP_M_MIN;
+  {
+    const size_t row_block_bytes = static_cast<size_t>(BM) * pr.K * ab_size;
+    while (p.group_m < 64 && 2 * static_cast<size_t>(p.group_m) * row_block_bytes <= GROUP_A_PANEL_BYTES && p.num_m_blocks > p.group_m) p.group_m *= 2;
+  }
   p.epi = epi;
   p.dev_status = ctx->dev_status;
   auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES, OUT_F32, TF32>;

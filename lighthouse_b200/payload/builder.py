@@ -43,6 +43,16 @@ class RegionBuilder:
     def truncf(self, a, dtype): return self._emit("arith.truncf", [a], dtype)
     def extf(self, a, dtype): return self._emit("arith.extf", [a], dtype)
 
+    def negf(self, a): return self._emit("arith.negf", [a], a.type)
+    def cos(self, a): return self._emit("math.cos", [a], a.type)
+    def sin(self, a): return self._emit("math.sin", [a], a.type)
+    def complex_create(self, re, im): return self._emit("complex.create", [re, im], f"complex<{re.type}>")
+    def complex_mul(self, a, b): return self._emit("complex.mul", [a, b], a.type)
+    def complex_re(self, a): return self._emit("complex.re", [a], a.type[len("complex<") : -1])
+    def complex_im(self, a): return self._emit("complex.im", [a], a.type[len("complex<") : -1])
+    def index(self, dim: int): return self._emit("linalg.index", [], "index", dim=int(dim))
+    def cmpi(self, pred, a, b): return self._emit("arith.cmpi", [a, b], "i1", predicate=pred)
+
     def cmpf(self, pred, a, b): return self._emit("arith.cmpf", [a, b], "i1", predicate=pred)
     def select(self, c, a, b): return self._emit("arith.select", [c, a, b], a.type)
 
@@ -106,6 +116,16 @@ class FuncBuilder:
     def transpose(self, x, out, permutation): return self._structured("linalg.transpose", [x], [out], permutation=list(permutation))
     def broadcast(self, x, out, dimensions): return self._structured("linalg.broadcast", [x], [out], dimensions=list(dimensions))
     def softmax(self, x, out, dimension: int): return self._structured("linalg.softmax", [x], [out], dimension=int(dimension))
+    def copy(self, x, out): return self._structured("linalg.copy", [x], [out])
+
+    def contract(self, a, b, out, maps):
+        """``linalg.contract``: multiply-accumulate over the dims that appear in ``a``'s and
+        ``b``'s maps but not in ``out``'s."""
+        return self._structured("linalg.contract", [a, b], [out], indexing_maps=list(maps))
+
+    def elementwise(self, kind: str, ins, out):
+        """``linalg.elementwise kind=#linalg.elementwise_kind<kind>`` (add, mul, square, rsqrt, ...)."""
+        return self._structured("linalg.elementwise", list(ins), [out], kind=kind)
 
     def generic(self, ins, outs, maps, iterator_types, body) -> Value | None:
         """``body(rb, *block_args)`` returns the value to yield; block args are the element

@@ -109,19 +109,34 @@ class Operation:
 
 @dataclass(eq=False)
 class AffineMap:
-    """``affine_map<(d0, d1, ...) -> (exprs)>`` restricted to results that are single dims
-    (projected permutations), which is all the payload generics use."""
+    """``affine_map<(d0, d1, ...) -> (exprs)>`` with results that are single dims (projected
+    permutations, which is all the GPU payload generics use) and, for the Llama builders,
+    constants (``(d0, d1) -> (d0, 0)``) and floor divisions of a dim by a constant
+    (``d2 floordiv 4``). ``results[i]`` is the dim index of result i (-1 for a constant);
+    ``special`` holds, per result index, ``("const", value)`` or ``("floordiv", divisor)``."""
 
     n_dims: int
     results: tuple[int, ...]  # dim index per result
+    special: dict = field(default_factory=dict)
+
+    def _expr(self, i: int) -> str:
+        sp = self.special.get(i)
+        if sp is None:
+            return f"d{self.results[i]}"
+        if sp[0] == "const":
+            return str(sp[1])
+        return f"d{self.results[i]} floordiv {sp[1]}"
 
     def __str__(self) -> str:
         dims = ", ".join(f"d{i}" for i in range(self.n_dims))
-        res = ", ".join(f"d{i}" for i in self.results)
+        res = ", ".join(self._expr(i) for i in range(len(self.results)))
         return f"affine_map<({dims}) -> ({res})>"
 
+    def is_plain(self) -> bool:
+        return not self.special
+
     def is_identity(self) -> bool:
-        return self.results == tuple(range(self.n_dims))
+        return not self.special and self.results == tuple(range(self.n_dims))
 
 
 @dataclass(eq=False)

@@ -66,7 +66,10 @@ def _expr_of_region(op: Operation, env: dict) -> tuple:
         if inner.name == "arith.constant":
             table[id(inner.result)] = ("const", float(inner.attrs["value"]))
             continue
-        extra = (inner.attrs.get("predicate"),) if inner.name == "arith.cmpf" else ()
+        if inner.name == "linalg.index":
+            table[id(inner.result)] = ("op", "linalg.index", int(inner.attrs["dim"]))
+            continue
+        extra = (inner.attrs.get("predicate"),) if inner.name in ("arith.cmpf", "arith.cmpi") else ()
         table[id(inner.result)] = ("op", inner.name) + extra + tuple(leaf(o) for o in inner.operands)
     raise UnsupportedPayload("linalg.generic body has no linalg.yield")
 
@@ -95,7 +98,10 @@ def _commutative_pair(e, pred_a, pred_b):
     return None
 
 
-class Recognizer:
+from .lower_llama import LlamaPatterns  # noqa: E402  (needs the helpers above)
+
+
+class Recognizer(LlamaPatterns):
     def __init__(self, func: Func):
         if func.body is None:
             raise UnsupportedPayload(f"function @{func.name} has no body")
@@ -130,6 +136,8 @@ class Recognizer:
             dst = self.plan.temp(tv.shape, tv.dtype)
             self.plan.elementwise("fill", dst, scalar=tv.scalar)
             return dst
+        if tv.kind == "empty":
+            raise UnsupportedPayload(f"{what}: reads an uninitialised tensor (tensor.empty)")
         raise UnsupportedPayload(f"{what}: operand is '{tv.kind}', expected a tensor with data")
 
     def dest_for(self, out_tv: TV, shape=None, dtype=None) -> PView:
@@ -195,6 +203,8 @@ class Recognizer:
         self.bind(op, TV("view", v.shape, v.dtype, v))
 
     def op_linalg_transpose(self, op):
+        if self.llama_transpose(op):
+            return
         src = self.as_view(self.tv(op.ins[0]), "linalg.transpose")
         v = src.permute(op.attrs["permutation"])
         out = self.tv(op.outs[0])
@@ -205,8 +215,10 @@ class Recognizer:
             self.bind(op, TV("view", v.shape, v.dtype, v))
 
     def op_linalg_broadcast(self, op):
-        src = self.as_view(self.tv(op.ins[0]), "linalg.broadcast")
         out_t = op.outs[0].type
+        if self.tv(op.ins[0]).kind == "fill":  # a broadcast constant is still that constant
+            return self.bind(op, TV("fill", out_t.shape, out_t.dtype, None, self.tv(op.ins[0]).scalar))
+        src = self.as_view(self.tv(op.ins[0]), "linalg.broadcast")
         v = src.broadcast_to(out_t.shape, set(op.attrs["dimensions"]))
         self.bind(op, TV("view", v.shape, v.dtype, v))
 
@@ -225,6 +237,8 @@ class Recognizer:
 
     def op_linalg_copy(self, op):
         src = self.as_view(self.tv(op.ins[0]), "linalg.copy")
+        if self.tv(op.outs[0]).kind == "empty" and op.results:  # copy into a fresh tensor: the source itself will do
+            return self.bind(op, TV("view", src.shape, src.dtype, src))
         dst = self.dest_for(self.tv(op.outs[0]))
         self.plan.elementwise("copy", dst, src)
         self.bind(op, TV("view", dst.shape, dst.dtype, dst))
@@ -306,6 +320,8 @@ class Recognizer:
     def op_linalg_max(self, op): self._binary(op, "max")
 
     def op_linalg_softmax(self, op):
+        if self.llama_softmax(op):
+            return
         x = self.as_view(self.tv(op.ins[0]), "linalg.softmax")
         if op.attrs.get("dimension") != x.rank - 1:
             raise UnsupportedPayload("linalg.softmax is only supported over the last dimension")
@@ -319,6 +335,8 @@ class Recognizer:
         maps: list[AffineMap] = op.attrs["indexing_maps"]
         iters = [str(i) for i in op.attrs["iterator_types"]]
         e = _expr_of_region(op, self.env)
+        if self.try_llama_generic(op, e, maps, iters):
+            return
         n_in = len(op.ins)
         out_val = op.outs[0]
         out_tv = self.tv(out_val)
@@ -562,8 +580,8 @@ def _fold_inplace_consumer(plan: Plan, i: int, g, d) -> bool:
         return False
     other = b if a == d else a
     n = d.shape[-1]
-    if ew == "act" and act == "relu" and not has_act and not has_res:
-        g.attrs["act"] = "relu"
+    if ew == "act" and (act == "relu" or d.dtype == "f32") and not has_act and not has_res:
+        g.attrs["act"] = act
     elif ew in ("add", "add_act") and other is not None and _is_row_vector_bcast(other, n) and not has_bias and not has_act and not has_res and d.rank == 2:
         g.operands[4] = PView(other.slot, (n,), (1,), other.dtype, other.offset)
         if ew == "add_act":
@@ -617,8 +635,10 @@ def fuse_gemm_epilogues(plan: Plan) -> int:
             ok = False
             if ew == "copy" and not has_res:  # cast (or plain copy): D takes the new type
                 ok = True
-            elif ew == "act" and act == "relu" and not has_act and not has_res:
-                g.attrs["act"] = "relu"
+            elif ew == "act" and (act == "relu" or out.dtype == "f32") and not has_act and not has_res:
+                # ReLU commutes with the rounding of a narrow result; any other activation is folded
+                # only where the un-fused sequence has no rounding in between (f32 results)
+                g.attrs["act"] = act
                 ok = True
             elif ew in ("add", "add_act") and _is_row_vector_bcast(other, n) and not has_bias and not has_act and not has_res and d.rank == 2:
                 bias = PView(other.slot, (n,), (1,), other.dtype, other.offset)

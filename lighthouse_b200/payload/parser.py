@@ -19,15 +19,15 @@ _WS = re.compile(r"(?:\s+|//[^\n]*)*")
 _SSA = re.compile(r"%[A-Za-z0-9_$.\-]+(?:#\d+)?")
 _IDENT = re.compile(r"[A-Za-z_][A-Za-z0-9_$.]*")
 _NUMBER = re.compile(r"[-+]?(?:0x[0-9a-fA-F]+|(?:\d+\.\d*|\.\d+|\d+)(?:[eE][-+]?\d+)?|inf|nan)")
-_SCALAR_TYPE = re.compile(r"(?:bf16|f16|f32|f64|index|i\d+)\b")
+_SCALAR_TYPE = re.compile(r"(?:complex<(?:bf16|f16|f32|f64)>|(?:bf16|f16|f32|f64|index|i\d+)\b)")
 
 ELEMENTWISE_BINARY = {"add", "sub", "mul", "div", "max", "min"}
 ELEMENTWISE_UNARY = {"exp", "log", "abs", "negf", "tanh", "erf", "sqrt", "rsqrt", "floor", "ceil", "square", "reciprocal"}
 REGION_BINARY = {
     "arith.addf", "arith.subf", "arith.mulf", "arith.divf", "arith.maximumf", "arith.maxnumf", "arith.minimumf", "arith.minnumf",
-    "arith.addi", "arith.muli", "arith.subi",
+    "arith.addi", "arith.muli", "arith.subi", "complex.mul",
 }
-REGION_UNARY = {"arith.negf", "math.rsqrt", "math.sqrt", "math.exp", "math.tanh", "math.erf", "math.log", "math.absf", "math.exp2"}
+REGION_UNARY = {"arith.negf", "math.rsqrt", "math.sqrt", "math.exp", "math.tanh", "math.erf", "math.log", "math.absf", "math.exp2", "math.cos", "math.sin"}
 REGION_CAST = {"arith.truncf", "arith.extf", "arith.sitofp", "arith.uitofp", "arith.fptosi", "arith.index_cast", "arith.bitcast"}
 
 
@@ -151,12 +151,13 @@ class _Parser:
 
     def _shaped(self, kind: str, inner: str) -> ShapedType:
         head, _, layout = inner.partition(",")
-        parts = head.strip().split("x")
-        dtype = parts[-1].strip()
+        head = head.strip()
+        tail = re.search(r"(complex<\w+>|bf16|f16|f32|f64|index|i\d+)$", head)  # the element type may itself contain an 'x'
+        dtype = tail.group(1) if tail else ""
         if not _SCALAR_TYPE.fullmatch(dtype):
             raise ParseError(f"unsupported element type in {kind}<{inner}>")
         dims = []
-        for d in parts[:-1]:
+        for d in [x for x in head[: tail.start()].split("x") if x.strip()]:
             d = d.strip()
             if d == "?":
                 raise ParseError(f"dynamic shapes are not supported: {kind}<{inner}>")
@@ -191,14 +192,22 @@ class _Parser:
         if not m:
             raise ParseError(f"unsupported affine_map<{inner}>")
         dims = [d.strip() for d in m.group(1).split(",") if d.strip()]
-        results = []
+        results, special = [], {}
         for r in (x.strip() for x in m.group(2).split(",")):
             if not r:
                 continue
-            if r not in dims:
-                raise ParseError(f"affine_map result '{r}' is not a plain dimension")
-            results.append(dims.index(r))
-        return AffineMap(len(dims), tuple(results))
+            fd = re.fullmatch(r"(\w+)\s+floordiv\s+(\d+)", r)
+            if r in dims:
+                results.append(dims.index(r))
+            elif re.fullmatch(r"-?\d+", r):
+                special[len(results)] = ("const", int(r))
+                results.append(-1)
+            elif fd and fd.group(1) in dims:
+                special[len(results)] = ("floordiv", int(fd.group(2)))
+                results.append(dims.index(fd.group(1)))
+            else:
+                raise ParseError(f"affine_map result '{r}' is not a dimension, a constant or 'dim floordiv constant'")
+        return AffineMap(len(dims), tuple(results), special)
 
     # ------------------------------------------------------------------------- values
     def define(self, name: str, type_, owner=None) -> Value:
@@ -374,7 +383,7 @@ class _Parser:
         if handler is not None:
             types = handler(op)
         elif name.startswith("linalg.") and name.split(".", 1)[1] in (
-            ELEMENTWISE_BINARY | ELEMENTWISE_UNARY | {"matmul", "batch_matmul", "fill", "transpose", "broadcast", "softmax", "generic", "copy", "matmul_transpose_b", "matmul_transpose_a", "batch_matmul_transpose_b"}
+            ELEMENTWISE_BINARY | ELEMENTWISE_UNARY | {"matmul", "batch_matmul", "fill", "transpose", "broadcast", "softmax", "generic", "copy", "matmul_transpose_b", "matmul_transpose_a", "batch_matmul_transpose_b", "contract", "elementwise"}
         ):
             types = self._linalg_structured(op)
         elif name in REGION_BINARY:
@@ -451,6 +460,12 @@ class _Parser:
                 self.expect("(")
                 op.attrs["dimension"] = self.integer()
                 self.expect(")")
+            elif self.accept_word("kind"):
+                self.expect("=")
+                m = self.rx(re.compile(r"#linalg\.elementwise_kind<(\w+)>"))
+                if not m:
+                    self.fail("expected #linalg.elementwise_kind<...>")
+                op.attrs["kind"] = m.group(1)
             else:
                 break
         ins, outs = [], []
@@ -563,6 +578,36 @@ class _Parser:
         op.attrs["dim"] = self.integer()
         self.expect(":")
         return [self.type()]
+
+    def _op_arith_cmpi(self, op):
+        op.attrs["predicate"] = self.ident()
+        self.expect(",")
+        a = self.ssa_use()
+        self.expect(",")
+        b = self.ssa_use()
+        self.expect(":")
+        self.type()
+        op.operands = [a, b]
+        return ["i1"]
+
+    def _op_complex_create(self, op):
+        a = self.ssa_use()
+        self.expect(",")
+        b = self.ssa_use()
+        self.expect(":")
+        t = self.type()
+        op.operands = [a, b]
+        return [t]
+
+    def _complex_part(self, op):
+        a = self.ssa_use()
+        self.expect(":")
+        t = self.type()  # the operand's complex type
+        op.operands = [a]
+        return [t[len("complex<") : -1]]
+
+    _op_complex_re = _complex_part
+    _op_complex_im = _complex_part
 
     def _op_arith_cmpf(self, op):
         op.attrs["predicate"] = self.ident()

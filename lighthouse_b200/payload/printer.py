@@ -50,12 +50,24 @@ def _print_op(op: Operation, ind: str, out: list[str]) -> None:
         out.append(f"{ind}{res}arith.constant {txt} : {t}")
     elif n == "tensor.empty":
         out.append(f"{ind}{res}tensor.empty() : {op.results[0].type}")
+    elif n == "complex.create":
+        out.append(f"{ind}{res}complex.create {_names(op.operands)} : {op.results[0].type}")
+    elif n in ("complex.re", "complex.im"):
+        out.append(f"{ind}{res}{n} {op.operands[0].name} : {op.operands[0].type}")
+    elif n == "complex.mul":
+        out.append(f"{ind}{res}complex.mul {_names(op.operands)} : {op.results[0].type}")
+    elif n == "arith.cmpi":
+        out.append(f"{ind}{res}arith.cmpi {op.attrs['predicate']}, {_names(op.operands)} : {op.operands[0].type}")
     elif n.startswith("linalg.") and n not in ("linalg.yield", "linalg.index"):
         head = f"{ind}{res}{n}"
         if n == "linalg.generic":
             maps = "[" + ", ".join(str(m) for m in op.attrs["indexing_maps"]) + "]"
             iters = "[" + ", ".join(f'"{i}"' for i in op.attrs["iterator_types"]) + "]"
             head += f" {{indexing_maps = {maps}, iterator_types = {iters}}}"
+        if n == "linalg.contract":
+            head += " indexing_maps = [" + ", ".join(str(m) for m in op.attrs["indexing_maps"]) + "]"
+        if n == "linalg.elementwise":
+            head += f" kind=#linalg.elementwise_kind<{op.attrs['kind']}>"
         if n == "linalg.softmax":
             head += f" dimension({op.attrs['dimension']})"
         if op.ins:
@@ -72,6 +84,8 @@ def _print_op(op: Operation, ind: str, out: list[str]) -> None:
             out.append(f"{ind}}}{tail}")
         else:
             out.append(head + tail)
+    elif n == "linalg.index":
+        out.append(f"{ind}{res}linalg.index {op.attrs['dim']} : index")
     elif n == "linalg.yield":
         out.append(f"{ind}linalg.yield {_names(op.operands)} : {_types(op.operands)}" if op.operands else f"{ind}linalg.yield")
     elif n == "bufferization.to_tensor":

@@ -97,7 +97,7 @@ class CudaTileSelector:
             timings = {bn: float(measure(m, n, k, bn)) for bn in TILE_WIDTHS if bn <= max(64, 8 * math.ceil(n / 8))}
             best = min(timings, key=timings.get)
             entry = {"shape": [m, n, k], "tile_n": best, "tflops": round(2.0 * m * n * k / timings[best] / 1e12, 1),
-                     "seconds": {str(bn): t for bn, t in timings.items()}}
+                     "seconds": {str(bn): round(t, 9) for bn, t in timings.items()}, "source": "autotune"}
             self.db[_key(m, n, k)] = entry
             out.append({"layer_kind": "matmul", "shape": [m, n, k], "tile_n": best, "source": "autotune"})
         if save:
@@ -106,9 +106,10 @@ class CudaTileSelector:
         return out
 
 
-def measure_on_gpu(ctx, nruns: int = 10, nwarmup: int = 3, l2_flush_bytes: int = 256 << 20) -> Callable[[int, int, int, int], float]:
+def measure_on_gpu(ctx, nruns: int = 10, nwarmup: int = 3, l2_flush_bytes: int = 256 << 20, reserved_sms: int = 0) -> Callable[[int, int, int, int], float]:
     """The ``measure`` callback of ``CudaTileSelector.autotune`` on a CUDA context: seeded bf16
-    operands, one GEMM per launch, L2 flushed between launches."""
+    operands, one GEMM per launch, L2 flushed between launches. ``reserved_sms``: the SMs the
+    persistent grid leaves free, as in the overlapped tensor-parallel schedules."""
     import torch
 
     from ..plan import ArgSpec
@@ -120,12 +121,69 @@ def measure_on_gpu(ctx, nruns: int = 10, nwarmup: int = 3, l2_flush_bytes: int =
         b = (torch.randn(k, n, generator=g) * 0.02).to(torch.bfloat16).cuda()
         d = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
         plan = Plan("gemm", [ArgSpec((m, n), "bf16", "d"), ArgSpec((m, k), "bf16", "a"), ArgSpec((k, n), "bf16", "b")])
+        if reserved_sms:
+            plan.reserve_sms(reserved_sms)
         plan.gemm(plan.arg(0), plan.arg(1), plan.arg(2))
-        plan.ops[0].attrs["tile_n"] = tile_n
+        plan.ops[-1].attrs["tile_n"] = tile_n
+        if reserved_sms:
+            plan.reserve_sms(0)
         session = PlanSession(plan, ctx=ctx)
+        torch.cuda.synchronize()
         try:
             return float(session.benchmark([d, a, b], nruns=nruns, nwarmup=nwarmup, l2_flush_bytes=l2_flush_bytes).mean())
         finally:
             session.close()
 
     return measure
+
+
+def decoder_gemm_shapes() -> list[tuple[int, int, int, int]]:
+    """(M, N, K, reserved SMs) of the GEMMs the benchmark configurations launch whose tile width
+    is free (the SwiGLU product keeps its 256-wide tiles): the K sweep of the GEMM
+    configuration, the Llama stack at tensor-parallel degrees 1, 2, 4, 8 (micro-batches of half
+    the tokens and 8 reserved SMs where it is parallel), nanoGPT on one GPU and with its batch
+    split 2, 4 and 8 ways."""
+    shapes = [(4096, 4096, k, 0) for k in (512, 1024, 2048, 4096, 8192, 16384)]
+    for tp in (1, 2, 4, 8):
+        m, r = (16384, 0) if tp == 1 else (8192, 8)
+        q, kv, f = 4096 // tp, 1024 // tp, 14336 // tp
+        shapes += [(m, q + 2 * kv, 4096, r), (m, 4096, q, r), (m, 4096, f, r)]
+    for dp in (1, 2, 4, 8):
+        m = 16384 // dp
+        shapes += [(m, 2304, 768, 0), (m, 768, 768, 0), (m, 3072, 768, 0), (m, 768, 3072, 0), (m, 50304, 768, 0)]
+    return shapes
+
+
+def main(argv=None) -> int:
+    """``python -m lighthouse_b200.schedule.tile_selector --autotune`` measures every tile
+    width on the GPU for the benchmark configurations' GEMM shapes and rewrites the database."""
+    import argparse
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--autotune", action="store_true")
+    ap.add_argument("--db", default=None, help="database file to update (default: the packaged one)")
+    ap.add_argument("--device", type=int, default=0)
+    args = ap.parse_args(argv)
+    if not args.autotune:
+        ap.print_help()
+        return 0
+    from ..context import CudaContext
+
+    ctx = CudaContext(args.device)
+    sel = CudaTileSelector(args.db, sm_count=ctx.sm_count)
+    by_reserve: dict[int, list] = {}
+    for m, n, k, r in decoder_gemm_shapes():
+        by_reserve.setdefault(r, []).append((m, n, k))
+    for r, shapes in by_reserve.items():
+        for entry in sel.autotune(shapes, measure_on_gpu(ctx, reserved_sms=r)):
+            e = sel.db[_key(*entry["shape"])]
+            e["reserved_sms"] = r
+            print(f"{entry['shape']} reserved {r}: tile_n {entry['tile_n']}  {e['tflops']} TFLOP/s  {e['seconds']}", flush=True)
+    with open(sel.db_path, "w") as f:
+        json.dump(sorted(sel.db.values(), key=lambda e: e["shape"]), f, indent=1)
+    ctx.close()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -4,7 +4,7 @@ Run where the reference is mounted (it is not on the GPU box):
 
     python tests/golden/make_golden.py <path of the reference checkout>
 
-Three fixtures:
+Four fixtures:
 
 * ``lh_run_pipeline_check.json`` — the 16 known-answer row values of the reference's own
   ``lh-run`` test, read as text from test/run/pipeline-check.mlir (CHECK lines), with the
@@ -13,6 +13,9 @@ Three fixtures:
   (examples/llama/ref_model.py, imported and executed here): RMSNorm, rotary embedding,
   Attention, FeedForward, TransformerBlock and a 2-layer Transformer trunk, on small seeded
   f32 configurations. These pin the oracle's Llama restatement against the reference itself.
+* ``llama_linalg_ref.npz`` — the same torch model run the way the reference's tests of its
+  linalg Llama builders run it (real frequency table, additive mask): see
+  ``golden_llama_linalg``.
 * ``numpy_checks.npz`` — inputs and outputs of the reference's own pure-numpy check code:
   ``_ln``, ``_f16``, ``_mha``, ``numpy_ref_block_fused``, ``numpy_ref_gpt_fused``
   (examples/xegpu/nanoGPT.py:84-135), ``check_correctness`` of fused_attention.py:46-106,
@@ -126,6 +129,49 @@ def golden_llama(ref: Path) -> None:
         out[f"tf_l{i}_ffn_norm"] = layer.ffn_norm.weight.detach().numpy()
     out["meta"] = np.array([args.dim, args.n_layers, args.n_heads, args.n_kv_heads, B, S], dtype=np.int64)
     np.savez_compressed(HERE / "llama_ref.npz", **out)
+
+
+def golden_llama_linalg(ref: Path) -> None:
+    """The configuration of the reference's own test_transformer_block_fwd / test_transformer_fwd
+    (examples/llama/test_llama3.py:1655-1985): the torch model run with the REAL frequency table
+    those tests feed it (a complex tensor with zero imaginary part, so the "rotary embedding" is
+    a plain scaling of the (even, odd) pairs), an additive -inf upper-triangular mask, unit norm
+    weights and no biases. These are the outputs the reference's linalg builders are checked
+    against, so they pin the oracle's restatement of those builders."""
+    spec = importlib.util.spec_from_file_location("ref_model", ref / "examples/llama/ref_model.py")
+    rm = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rm)
+    torch.manual_seed(4321)
+    args = rm.ModelArgs(dim=64, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=97, multiple_of=16, norm_eps=1e-5, max_batch_size=2, max_seq_len=16)
+    B, S = 2, 8
+    hd = args.dim // args.n_heads
+    out: dict[str, np.ndarray] = {}
+    model = rm.Transformer(args)
+    for name, prm in model.named_parameters():
+        if prm.ndim > 1:
+            with torch.no_grad():
+                prm.copy_(torch.randn_like(prm) * 0.2)
+    x = torch.randn(B, S, args.dim)
+    freqs_real = torch.randn(S, hd // 2)
+    freqs = torch.complex(freqs_real, torch.zeros_like(freqs_real))
+    mask = torch.triu(torch.full((B, args.n_heads, S, S), float("-inf")), diagonal=1)
+    with torch.no_grad():
+        attn_out = model.layers[0].attention(x, 0, freqs, mask)
+        h = x
+        blocks = []
+        for layer in model.layers:
+            h = layer(h, 0, freqs, mask)
+            blocks.append(h)
+        final = model.norm(h)
+    out["x"], out["freqs_real"], out["mask"] = x.numpy(), freqs_real.numpy(), mask.numpy()
+    out["attn_out"], out["block0_out"], out["out"] = attn_out.numpy(), blocks[0].numpy(), final.numpy()
+    for i, layer in enumerate(model.layers):
+        for n in ("wq", "wk", "wv", "wo"):
+            out[f"l{i}_{n}"] = getattr(layer.attention, n).weight.detach().numpy()
+        for n in ("w1", "w2", "w3"):
+            out[f"l{i}_{n}"] = getattr(layer.feed_forward, n).weight.detach().numpy()
+    out["meta"] = np.array([args.dim, args.n_layers, args.n_heads, args.n_kv_heads, B, S, out["l0_w1"].shape[0]], dtype=np.int64)
+    np.savez_compressed(HERE / "llama_linalg_ref.npz", **out)
 
 
 class _RecordingNumpy:
@@ -276,4 +322,5 @@ if __name__ == "__main__":
     golden_lh_run(ref)
     golden_llama(ref)
     golden_numpy_checks(ref)
+    golden_llama_linalg(ref)
     print("wrote", sorted(p.name for p in HERE.iterdir()))

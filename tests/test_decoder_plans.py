@@ -122,11 +122,20 @@ def _tp_worker(rank, world, port, q):
         logits = run_gpt_rank(GPT, w, ids, rank, world, allreduce)
         w4, ids4 = gpt_inputs(GPT4)
         logits_overlapped = run_gpt_rank(GPT4, w4, ids4, rank, world, allreduce, overlapped=True)
+        # batch split: this rank's sequences through the plain single-rank plan, no collective;
+        # the ranks' logits are gathered only to be checked
+        import dataclasses
+
+        part = dataclasses.replace(GPT4, batch=GPT4.batch // world)
+        mine = run_gpt_rank(part, w4, ids4[rank * part.tokens : (rank + 1) * part.tokens], 0, 1)
+        gathered = [torch.zeros(mine.shape, dtype=torch.float32) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(np.ascontiguousarray(mine, dtype=np.float32)))
+        logits_dp = torch.cat(gathered, dim=0).numpy()
         lw, x = llama_inputs(LLAMA)
         hidden = run_llama_rank(LLAMA, lw, x, rank, world, allreduce)
         hidden_overlapped = run_llama_rank(LLAMA, lw, x, rank, world, allreduce, overlapped=True)
         hidden_fused = run_llama_rank(LLAMA, lw, x, rank, world, allreduce, overlapped=True, fused=True)
-        q.put((rank, logits, hidden, hidden_overlapped, hidden_fused, logits_overlapped))
+        q.put((rank, logits, hidden, hidden_overlapped, hidden_fused, logits_overlapped, logits_dp))
     finally:
         dist.destroy_process_group()
 
@@ -152,7 +161,9 @@ def test_two_rank_tensor_parallel_matches_single_rank():
     w4, ids4 = gpt_inputs(GPT4)
     logits4 = np.concatenate([r[5] for r in results], axis=1)
     assert max_rel_err(logits4, gpt_reference(GPT4, w4, ids4)) < 2e-2  # row-sharded residual, overlapped collectives
-    for _, _, hidden, hidden_overlapped, hidden_fused, _ in results:  # the residual stream is replicated after each all-reduce
+    for r in results:  # sequences split over the ranks: every rank's gathered logits are the full batch's
+        assert max_rel_err(r[6], gpt_reference(GPT4, w4, ids4)) < 2e-2
+    for _, _, hidden, hidden_overlapped, hidden_fused, _, _ in results:  # the residual stream is replicated after each all-reduce
         assert max_rel_err(hidden, want) < 2e-2
         assert max_rel_err(hidden_overlapped, want) < 2e-2  # reduce-scatter / all-gather schedule
         assert max_rel_err(hidden_fused, want) < 2e-2  # one fused reduce + norm + gather per sub-block

@@ -81,6 +81,49 @@ def test_runner_gpu_memory_manager_and_callback(ctx):
     runner.close()
 
 
+@pytest.mark.parametrize("transpose_b,accumulate_c,hidden", [(False, False, [384, 640]), (True, False, [384, 640]), (False, True, []), (True, True, [])])
+def test_mlp_payload_three_layers_through_runner(ctx, transpose_b, accumulate_c, hidden):
+    """The chained MLP payload (generate_gpu_mlp_payload of the reference,
+    lighthouse/ingress/mlir_gen/gpu_mlp_payload.py:10-107: three layers, bias, ReLU between
+    layers, hidden activations never leaving the device) through the Runner with
+    GPUMemoryManager, checked the way examples/xegpu/mlp.py:47-101 checks it: every layer's
+    result truncated to the operand type, ReLU on all but the last. ``accumulate_c`` is run
+    on the single-layer form: with hidden layers the reference's payload accumulates those
+    into a ``tensor.empty`` (gpu_mlp_payload.py:83-88), whose content is undefined; this
+    backend refuses that payload with a ValueError instead of reading uninitialised memory."""
+    from lighthouse_b200.payload import generators as G
+    from lighthouse_b200.utils.numpy import mlir_to_numpy_dtype
+
+    batch, sizes = 256, [512] + hidden + [128]
+    nl = len(sizes) - 1
+    m = G.generate_gpu_mlp_payload("payload", batch, sizes[0], sizes[-1], sizes[1:-1], "bf16", "f32", "bf16", "bf16", False, transpose_b, True, True, accumulate_c)
+    if accumulate_c:
+        with pytest.raises(ValueError, match="uninitialised"):
+            Runner(G.generate_gpu_mlp_payload("payload", batch, 512, 128, [384], "bf16", "f32", "bf16", "bf16", False, transpose_b, True, True, True), context=ctx)
+    bf16 = mlir_to_numpy_dtype("bf16")
+    rng = np.random.RandomState(11)
+    x = (rng.rand(batch, sizes[0]) - 0.5).astype(bf16)
+    ws = [(rng.rand(sizes[i], sizes[i + 1]) - 0.5).astype(bf16) for i in range(nl)]
+    bs = [(rng.rand(sizes[i + 1]) - 0.5).astype(bf16) for i in range(nl)]
+    c0 = (rng.rand(batch, sizes[-1]) - 0.5).astype(bf16) if accumulate_c else np.zeros((batch, sizes[-1]), bf16)
+    host_ws = [np.ascontiguousarray(w.T) for w in ws] if transpose_b else ws
+    out = np.zeros_like(c0)
+    runner = Runner(m, mem_manager_cls=GPUMemoryManager, context=ctx)
+    plan = runner.payload.plans["payload"]
+    launches = ctx.launch_count
+    runner.execute("payload", [c0, x] + host_ws + bs, Runner.get_gpu_argument_access_callback(out))
+    if not accumulate_c:
+        # one kernel per layer with its epilogue fused; hidden activations are device temporaries
+        assert [op.kind for op in plan.ops] == ["gemm"] * nl
+        assert ctx.launch_count - launches == nl
+    f = lambda a: np.asarray(a, dtype=np.float32)
+    h = f(x)
+    for i in range(nl):
+        h = R.gemm_epilogue(h, f(ws[i]), c=f(c0) if (accumulate_c and i == nl - 1) else None, bias=f(bs[i]), act="relu" if i < nl - 1 else "none", out_dtype="bf16")
+    assert_parity(f(out), h, "bf16")
+    runner.close()
+
+
 @pytest.mark.parametrize("init_int", [True, False])
 def test_matmul_example_defaults_accumulate_c(ctx, init_int):
     """The reference example's default: accumulate into a random C (exact with integer inputs)."""

@@ -222,3 +222,17 @@ def test_causal_prefix_property_of_the_decoder_oracles():
     full = R.nanogpt_forward(xe, gn["layers"], gn["gf_g"], gn["gf_b"], gn["lmw"], gn["lmb"], g.n_head, g.eps, True, g.act, "bf16", g.batch)
     got = P.nanogpt_prefix_reference(gw, ids, g, (1, 2), 7, vocab_slice=slice(48, 96))
     assert max_rel_err(got, full[P.prefix_rows(g.seq, (1, 2), 7), 48:96]) <= 1e-6
+
+
+def test_llama_linalg_restatement_matches_the_reference_tests_ground_truth():
+    """The oracle's restatement of the reference's linalg Llama builders against the torch
+    model run the way the reference's own tests run it (real frequencies, additive mask):
+    attention, one block, the two-layer transformer. Tolerance: the oracle's f32 bound, far
+    inside the 0.01 the reference's tests allow (examples/llama/test_llama3.py:1651,1812,1985)."""
+    g = np.load(os.path.join(GOLDEN, "llama_linalg_ref.npz"))
+    dim, nl, nh, nkv, B, S, hidden = (int(v) for v in g["meta"])
+    layers = [{k: g[f"l{i}_{k}"] for k in ("wq", "wk", "wv", "wo", "w1", "w2", "w3")} for i in range(nl)]
+    l0 = layers[0]
+    assert_close(R.llama_linalg_attention(g["x"], l0["wq"], l0["wk"], l0["wv"], l0["wo"], g["freqs_real"], g["mask"], nh, nkv), g["attn_out"], "f32", "get_attention")
+    assert_close(R.llama_linalg_block(g["x"], l0, g["freqs_real"], g["mask"], nh, nkv), g["block0_out"], "f32", "get_transformer_block")
+    assert_close(R.llama_linalg_transformer(g["x"], layers, g["freqs_real"], g["mask"], nh, nkv), g["out"], "f32", "get_transformer")
