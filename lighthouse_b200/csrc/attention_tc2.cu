@@ -16,7 +16,6 @@
 #include "common.cuh"
 #include "epilogue.cuh"
 #include "ptx.cuh"
-#include <stdlib.h>
 
 namespace lh {
 
@@ -57,76 +56,6 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// 2^x for a pair on the FMA pipe instead of the special-function unit (which the softmax
-// saturates: 16 results per clock per SM): x = n + r with n the nearest integer and r in
-// [-0.5, 0.5], 2^r as a degree-3 polynomial (relative error 1e-4, far below the bf16 rounding
-// P gets next), n added into the exponent field. x is clamped at -126 so the exponent cannot
-// wrap; such values are 2^-126 instead of 0, which no bf16 sum can see.
-__device__ __forceinline__ uint64_t exp2_poly_pair(uint64_t x2) {
-  float x0, x1;
-  f32x2_unpack(x2, x0, x1);
-  x2 = f32x2_pack(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
-  const uint64_t magic = f32x2_pack(12582912.f, 12582912.f);  // 1.5 * 2^23: the sum's low mantissa bits are n
-  const uint64_t t2 = f32x2_add(x2, magic);
-  const uint64_t r2 = f32x2_sub(x2, f32x2_sub(t2, magic));
-  uint64_t p2 = f32x2_fma(r2, f32x2_pack(0.05583828315138817f, 0.05583828315138817f), f32x2_pack(0.2426394820213318f, 0.2426394820213318f));
-  p2 = f32x2_fma(p2, r2, f32x2_pack(0.6931367516517639f, 0.6931367516517639f));
-  p2 = f32x2_fma(p2, r2, f32x2_pack(0.9999245405197144f, 0.9999245405197144f));
-  float t0, t1, p0, p1;
-  f32x2_unpack(t2, t0, t1);
-  f32x2_unpack(p2, p0, p1);
-  p0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
-  p1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
-  return f32x2_pack(p0, p1);
-}
-
-// Running maxima of 32 scores, four independent chains of three-input max.
-__device__ __forceinline__ void chunk_max(const uint32_t (&s)[32], float& m0, float& m1, float& m2, float& m3) {
-#pragma unroll
-  for (int i = 0; i < 32; i += 8) {
-    m0 = fmax3(m0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-    m1 = fmax3(m1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-    m2 = fmax3(m2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-    m3 = fmax3(m3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
-  }
-}
-__device__ __forceinline__ void chunk_mask(uint32_t (&s)[32], int first_col, int limit) {
-#pragma unroll
-  for (int i = 0; i < 32; ++i)
-    if (first_col + i > limit) s[i] = 0xff800000u;  // -inf
-}
-
-// 32 scores -> 16 packed bf16 pairs of P = 2^(scale * s - m), and their sum into two packed
-// accumulators. POLY of every 4 pairs take the polynomial path.
-template <int POLY>
-__device__ __forceinline__ void chunk_exp(const uint32_t (&s)[32], uint32_t (&pk)[16], uint64_t scale2, uint64_t negm2, uint64_t& acc_a,
-                                          uint64_t& acc_b, bool need_mask, int first_col, int limit) {
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const uint64_t x2 = f32x2_fma(f32x2_pack(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), scale2, negm2);
-    uint64_t p2;
-    float p0, p1;
-    if ((i & 3) < POLY) {
-      p2 = exp2_poly_pair(x2);
-      f32x2_unpack(p2, p0, p1);
-    } else {
-      float x0, x1;
-      f32x2_unpack(x2, x0, x1);
-      p0 = ex2(x0);
-      p1 = ex2(x1);
-      p2 = f32x2_pack(p0, p1);
-    }
-    if (need_mask) {
-      p0 = (first_col + 2 * i <= limit) ? p0 : 0.f;
-      p1 = (first_col + 2 * i + 1 <= limit) ? p1 : 0.f;
-      p2 = f32x2_pack(p0, p1);
-    }
-    if (i & 1) acc_b = f32x2_add(acc_b, p2);
-    else acc_a = f32x2_add(acc_a, p2);
-    pk[i] = pack_bf16x2(p0, p1);
-  }
-}
-
 __device__ __forceinline__ bool wait_warp2(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* dev_status,
                                            int code, int lane) {
   // every lane observes the phase itself (its later reads are ordered after it); the warp
@@ -136,21 +65,11 @@ __device__ __forceinline__ bool wait_warp2(uint64_t* bar, uint32_t parity, volat
   return __all_sync(0xffffffffu, ok);
 }
 
-// VAR selects the data path of the softmax warps and the MMA warp's pacing:
-//   bit 0   the next Q K^T is issued without waiting for the previous P V to complete (the
-//           tensor core runs one thread's MMAs in issue order, and P V reads the columns
-//           the next Q K^T overwrites before that one can start)
-//   bit 1   softmax on 32-column chunks with the next chunk's tensor-memory load in flight
-//           under the current chunk's arithmetic, packed f32x2 multiply-add / add, 3-input max
-//   bits 2-3  how many of every four pairs of exponentials run as polynomials on the FMA pipe
-template <int HD, int VAR>
+template <int HD>
 __global__ void __launch_bounds__(ATT2_THREADS, 2)
 attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const Attn2Params p) {
   using L = Attn2Smem<HD>;
-  constexpr bool NOWAIT_PV = (VAR & 1) != 0;
-  constexpr bool CHUNKED = (VAR & 2) != 0;
-  constexpr int POLY = (VAR >> 2) & 3;
   constexpr int TMEM_COLS = 256;
   constexpr uint32_t S_COL = 0, O_COL = 128;  // P (bf16 pairs) overwrites S columns [0, 64)
   extern __shared__ uint8_t smem_raw[];
@@ -285,7 +204,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         umma_commit(pv_done);
         // The next Q K^T overwrites the columns this product reads P from; the two MMAs use
         // different accumulators, so wait for this one instead of relying on issue order.
-        if (!NOWAIT_PV && j + 1 < n_kv && !mbar_wait(pv_done, ph, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) break;
+        if (j + 1 < n_kv && !mbar_wait(pv_done, ph, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) break;
       }
     }
   } else {
@@ -310,25 +229,6 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int limit = need_mask ? (p.causal ? min(p.Skv - 1, q_row + offset) : (p.Skv - 1)) - col0 : BKV2;  // last visible column in this tile
       // pass 1: row max of the scores
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;  // independent chains
-      if (CHUNKED) {
-        uint32_t ca[32], cb[32];
-        tmem_ld_32x32b_x32(s_addr, ca);
-        tmem_ld_wait();
-        tmem_ld_32x32b_x32(s_addr + 32, cb);
-        if (need_mask) chunk_mask(ca, 0, limit);
-        chunk_max(ca, mx0, mx1, mx2, mx3);
-        tmem_ld_wait();
-        tmem_ld_32x32b_x32(s_addr + 64, ca);
-        if (need_mask) chunk_mask(cb, 32, limit);
-        chunk_max(cb, mx0, mx1, mx2, mx3);
-        tmem_ld_wait();
-        tmem_ld_32x32b_x32(s_addr + 96, cb);
-        if (need_mask) chunk_mask(ca, 64, limit);
-        chunk_max(ca, mx0, mx1, mx2, mx3);
-        tmem_ld_wait();
-        if (need_mask) chunk_mask(cb, 96, limit);
-        chunk_max(cb, mx0, mx1, mx2, mx3);
-      } else {
 #pragma unroll
       for (int c = 0; c < 4; c += 2) {
         uint32_t s0[32], s1[32];
@@ -349,7 +249,6 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mx2 = fmaxf(mx2, __uint_as_float(s1[i]));
           mx3 = fmaxf(mx3, __uint_as_float(s1[i + 1]));
         }
-      }
       }
       float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       mx *= p.scale_log2;  // scale > 0: max commutes with the scaling
@@ -377,37 +276,6 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // half (64 keys) is handed to the MMA warp as soon as it is in tensor memory
       const float msub = (m_used == -INFINITY) ? 0.f : m_used;
       float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
-      if (CHUNKED) {
-        const uint64_t scale2 = f32x2_pack(p.scale_log2, p.scale_log2), negm2 = f32x2_pack(-msub, -msub);
-        uint64_t acc_a = 0ull, acc_b = 0ull;  // two packed accumulators: four independent sums
-        uint32_t ca[32], cb[32], pk[16];
-        tmem_ld_32x32b_x32(s_addr, ca);
-        tmem_ld_wait();
-        // chunk c holds keys [32c, 32c + 32); its P goes to columns [16c, 16c + 16), which lie
-        // inside score columns already loaded
-        tmem_ld_32x32b_x32(s_addr + 32, cb);
-        chunk_exp<POLY>(ca, pk, scale2, negm2, acc_a, acc_b, need_mask, 0, limit);
-        tmem_st_32x32b_x16(s_addr, pk);
-        tmem_ld_wait();
-        tmem_ld_32x32b_x32(s_addr + 64, ca);
-        chunk_exp<POLY>(cb, pk, scale2, negm2, acc_a, acc_b, need_mask, 32, limit);
-        tmem_st_32x32b_x16(s_addr + 16, pk);
-        tmem_st_wait();
-        tc_fence_before_sync();
-        mbar_arrive(&p_half[0]);
-        tmem_ld_wait();
-        tmem_ld_32x32b_x32(s_addr + 96, cb);
-        chunk_exp<POLY>(ca, pk, scale2, negm2, acc_a, acc_b, need_mask, 64, limit);
-        tmem_st_32x32b_x16(s_addr + 32, pk);
-        tmem_ld_wait();
-        chunk_exp<POLY>(cb, pk, scale2, negm2, acc_a, acc_b, need_mask, 96, limit);
-        tmem_st_32x32b_x16(s_addr + 48, pk);
-        tmem_st_wait();
-        tc_fence_before_sync();
-        mbar_arrive(&p_half[1]);
-        f32x2_unpack(acc_a, rs0, rs1);
-        f32x2_unpack(acc_b, rs2, rs3);
-      } else {
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         uint32_t s0[32], s1[32];
@@ -439,7 +307,6 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_st_wait();
         tc_fence_before_sync();
         mbar_arrive(&p_half[hf]);
-      }
       }
       l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
     }
@@ -478,7 +345,7 @@ attn_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 }
 
-template <int HD, int VAR>
+template <int HD>
 int launch2_hd(lh_ctx* ctx, const AttnProblem& a) {
   using L = Attn2Smem<HD>;
   CUtensorMap tmQ, tmK, tmV;
@@ -505,7 +372,7 @@ int launch2_hd(lh_ctx* ctx, const AttnProblem& a) {
   p.causal = a.causal;
   p.num_q_tiles = (a.Sq + BQ2 - 1) / BQ2;
   p.dev_status = ctx->dev_status;
-  auto kernel = attn_fwd_tc2_kernel<HD, VAR>;
+  auto kernel = attn_fwd_tc2_kernel<HD>;
   LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   const int64_t grid = static_cast<int64_t>(a.B) * a.Hq * p.num_q_tiles;
   p.pair_slots = (grid > ctx->sm_count && grid <= 2 * static_cast<int64_t>(ctx->sm_count)) ? ctx->sm_count : 0;
@@ -518,23 +385,8 @@ int launch2_hd(lh_ctx* ctx, const AttnProblem& a) {
 
 int attn_tc2_launch(lh_ctx* ctx, const AttnProblem& a) {
   if (a.scale <= 0.f) return set_error(ctx, LH_ERR_UNSUPPORTED, "attention: scale must be positive");
-  // experiment switch (development only): which variant of the kernel runs
-  static const int var = getenv("LH_ATTN_VAR") ? atoi(getenv("LH_ATTN_VAR")) : 0;
-  if (a.D == 128) {
-    switch (var) {
-      case 1: return launch2_hd<128, 1>(ctx, a);
-      case 2: return launch2_hd<128, 2>(ctx, a);
-      case 3: return launch2_hd<128, 3>(ctx, a);
-      case 7: return launch2_hd<128, 7>(ctx, a);
-      case 11: return launch2_hd<128, 11>(ctx, a);
-      default: return launch2_hd<128, 0>(ctx, a);
-    }
-  }
-  switch (var) {
-    case 3: return launch2_hd<64, 3>(ctx, a);
-    case 7: return launch2_hd<64, 7>(ctx, a);
-    default: return launch2_hd<64, 0>(ctx, a);
-  }
+  if (a.D == 128) return launch2_hd<128>(ctx, a);
+  return launch2_hd<64>(ctx, a);
 }
 
 }  // namespace lh

@@ -1,32 +1,38 @@
-// Flash-attention forward, third-generation kernel: two query tiles per CTA in explicit
-// ping-pong, one CTA per SM.
+// Flash-attention forward: two query tiles per CTA in explicit ping-pong, one persistent CTA
+// per SM.
 //
 // Algorithm and numerics are those of attention_tc2.cu (online softmax of
 // replace_with_fused_attention.py:334-455 in the reference: f32 scores / max / sum /
 // accumulator, P rounded to bf16 before P.V, O = acc / l; P kept in tensor memory over the
-// score columns, TS-form MMA). What changes is who overlaps with whom. Two independent CTAs on
-// an SM run in phase: their MMAs share the tensor pipe at instruction granularity, so both
-// score tiles complete together, both softmaxes then share the special-function unit, and each
-// pipe idles while the other works (measured: tensor pipe 44 %, special-function pipe 45 %
-// busy, never together). Here ONE MMA warp serves two query tiles A and B of the same
-// (batch, head) and fixes the order
-//     ... P_A V -> Q_A K' -> P_B V -> Q_B K' -> P_A' V' -> ...
-// so that tile A's softmax runs exactly under tile B's two products and vice versa, and both
-// tiles read the same K / V tiles from shared memory (loaded once for 256 query rows).
+// score columns, TS-form MMA). What changes is the schedule:
+//   * ONE MMA warp serves two query tiles A and B of the same (batch, head) and fixes the order
+//         ... P_A V -> Q_A K' -> P_B V -> Q_B K' -> P_A' V' -> ...
+//     so that tile A's softmax runs under tile B's two products and vice versa, and both tiles
+//     read the same K / V tiles from shared memory (loaded once for 256 query rows). Two
+//     independent CTAs on an SM do not settle into that order by themselves.
+//   * The whole MMA warp walks the schedule and one elected lane issues, so descriptor
+//     arithmetic stays warp-uniform: an MMA of 128 x 128 x 16 runs for about 64 clocks, and a
+//     single divergent thread building two descriptors per instruction could not feed the
+//     tensor core that fast (measured: ~92 clocks per issue).
+//   * CTAs are persistent: a CTA walks work items (batch, head, pair of query tiles) with its
+//     barriers' phases running on. The next item's Q is fetched during the last key tiles of
+//     the current one, its first Q K^T is issued right behind the current item's last P V, and
+//     only the softmax warps' write-out of O (tensor memory -> registers -> global) separates
+//     two items, per tile and under the other tile's work. One CTA per work item left ~10 us of
+//     set-up and drain per item exposed (a quarter of the run at sequence length 2048).
 //
-// Warps: 0 TMA producer (Q_A, Q_B once; K and V in two-stage rings), 1 MMA issuer, 2-5 softmax
-// of tile A, 6-9 softmax of tile B (one row per thread). Tensor memory: S_A, S_B, O_A, O_B,
-// 128 columns each = all 512. Every wait is bounded.
+// Warps: 0 TMA producer (Q_A, Q_B per item; K and V in two-stage rings), 1 MMA issuer, 2-5
+// softmax of tile A, 6-9 softmax of tile B (one row per thread). Tensor memory: S_A, S_B, O_A,
+// O_B, 128 columns each = all 512. Every wait is bounded.
 #include "common.cuh"
 #include "epilogue.cuh"
 #include "ptx.cuh"
-#include <stdlib.h>
 
 namespace lh {
 
 namespace {
 
-constexpr int BQ3 = 128;   // query rows per tile; two tiles per CTA
+constexpr int BQ3 = 128;   // query rows per tile; two tiles per work item
 constexpr int BKV3 = 128;
 constexpr int ATT3_THREADS = 320;
 constexpr int SUBTILE3 = 128 * 128;  // 128 rows x 64 bf16
@@ -39,15 +45,9 @@ struct Attn3Params {
   float scale_log2;
   int causal;
   int num_q_pairs;
+  int num_items;  // B * Hq * num_q_pairs
   int* dev_status;
-  long long* dbg;  // development only: timeline of one block
-  int dbg_block;
 };
-
-#define DBG_MARK(j, slot)                                                                      \
-  do {                                                                                         \
-    if (p.dbg && blockIdx.x == p.dbg_block && (j) < 12) p.dbg[(j) * 16 + (slot)] = clock64();   \
-  } while (0)
 
 template <int HD>
 struct Attn3Smem {
@@ -57,7 +57,7 @@ struct Attn3Smem {
   static constexpr int K_OFF = Q_OFF + 2 * Q_BYTES;    // 2 stages
   static constexpr int V_OFF = K_OFF + 2 * KV_BYTES;   // 2 stages
   static constexpr int BAR_OFF = V_OFF + 2 * KV_BYTES;
-  static constexpr int NUM_BARS = 17;
+  static constexpr int NUM_BARS = 18;
   static constexpr int DYN_BYTES = BAR_OFF + NUM_BARS * 8 + 16 + 1024;
   static_assert(DYN_BYTES <= 232448, "exceeds the shared memory a CTA can opt into");
 };
@@ -75,7 +75,12 @@ __device__ __forceinline__ bool wait_warp3(uint64_t* bar, uint32_t parity, volat
   return __all_sync(0xffffffffu, ok);
 }
 
-// Key tiles a query tile starting at row q0 visits (0 if the tile lies outside the queries).
+// One work item: which (batch, query head, pair of query tiles), and how many key tiles each
+// of its two query tiles visits (0 for a tile that lies outside the queries).
+struct Item3 {
+  int b, hq, hkv, q0, n_a, n_b, n_max;
+};
+
 __device__ __forceinline__ int kv_tiles_for(const Attn3Params& p, int q0) {
   if (q0 >= p.Sq) return 0;
   int n = (p.Skv + BKV3 - 1) / BKV3;
@@ -86,10 +91,42 @@ __device__ __forceinline__ int kv_tiles_for(const Attn3Params& p, int q0) {
   return n;
 }
 
-// TV: timing experiments (development only). bit 0: no row-max pass (wrong results unless the
-// scores are small); bit 1: no exponentials (wrong results); bit 2: one pass over the scores
-// with the whole row in registers (correct).
-template <int HD, int TV>
+// Which item CTA `cta` of `grid` takes in round r, or -1 if none: rounds alternate direction
+// (c, 2 grid - 1 - c, 2 grid + c, ...). Causal items are numbered heaviest first (a pair of
+// query tiles (2i, 2i + 1) visits up to 2i + 2 key tiles), so a CTA that got an early, heavy
+// item of one round gets a late, light one of the next, and the CTAs' totals stay within a
+// few key tiles of each other (plain round-robin leaves 70 against a mean of 62 at batch 8,
+// 16 heads, sequence 2048; this order 64).
+__device__ __forceinline__ int item_of_round(int r, int cta, int grid, int num_items) {
+  const int idx = r * grid + ((r & 1) ? grid - 1 - cta : cta);
+  return idx < num_items ? idx : -1;
+}
+#define FOR_EACH_ITEM(item)                                                                          \
+  for (int r_ = 0, item = 0; r_ * static_cast<int>(gridDim.x) < p.num_items; ++r_)                     \
+    if ((item = item_of_round(r_, blockIdx.x, gridDim.x, p.num_items)) >= 0)
+
+__device__ __forceinline__ Item3 decode_item(const Attn3Params& p, int item) {
+  const int nbh = p.B * p.Hq;
+  int bh, qp;
+  if (p.causal) {
+    qp = p.num_q_pairs - 1 - item / nbh;
+    bh = item % nbh;
+  } else {
+    bh = item / p.num_q_pairs;
+    qp = item % p.num_q_pairs;
+  }
+  Item3 w;
+  w.b = bh / p.Hq;
+  w.hq = bh % p.Hq;
+  w.hkv = w.hq / (p.Hq / p.Hkv);
+  w.q0 = qp * (2 * BQ3);
+  w.n_a = kv_tiles_for(p, w.q0);
+  w.n_b = kv_tiles_for(p, w.q0 + BQ3);
+  w.n_max = max(w.n_a, w.n_b);
+  return w;
+}
+
+template <int HD>
 __global__ void __launch_bounds__(ATT3_THREADS, 1)
 attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const Attn3Params p) {
@@ -101,40 +138,24 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;    // [2] stages
-  uint64_t* k_empty = bars + 3;   // [2]
-  uint64_t* v_full = bars + 5;    // [2]
-  uint64_t* v_empty = bars + 7;   // [2]
-  uint64_t* s_full = bars + 9;    // [2] tiles
-  uint64_t* p_half = bars + 11;   // [tile][half]: keys [0,64) / [64,128) of P written
-  uint64_t* pv_done = bars + 15;  // [2] tiles
+  uint64_t* q_empty = bars + 1;   // the item's last Q K^T has read Q
+  uint64_t* k_full = bars + 2;    // [2] stages
+  uint64_t* k_empty = bars + 4;   // [2]
+  uint64_t* v_full = bars + 6;    // [2]
+  uint64_t* v_empty = bars + 8;   // [2]
+  uint64_t* s_full = bars + 10;   // [2] tiles
+  uint64_t* p_half = bars + 12;   // [tile][half]: keys [0,64) / [64,128) of P written
+  uint64_t* pv_done = bars + 16;  // [2] tiles
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // Work order: a causal pair of query tiles (2i, 2i + 1) visits up to 2i + 2 key tiles, so
-  // pairs are handed out heaviest first and the tail of the grid is made of short blocks.
-  int bh, qp;
-  if (p.causal) {
-    const int nbh = gridDim.x / p.num_q_pairs;
-    qp = p.num_q_pairs - 1 - blockIdx.x / nbh;
-    bh = blockIdx.x % nbh;
-  } else {
-    bh = blockIdx.x / p.num_q_pairs;
-    qp = blockIdx.x % p.num_q_pairs;
-  }
-  const int b = bh / p.Hq;
-  const int hq = bh % p.Hq;
-  const int hkv = hq / (p.Hq / p.Hkv);
-  const int q0 = qp * (2 * BQ3);
   const int offset = p.Skv - p.Sq;
-  const int n_a = kv_tiles_for(p, q0), n_b = kv_tiles_for(p, q0 + BQ3);
-  const int n_max = max(n_a, n_b);
-  auto n_of = [&](int t) { return t == 0 ? n_a : n_b; };
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
@@ -163,78 +184,112 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      // Both query tiles; rows beyond the queries arrive as zeros (their results are never stored).
-      mbar_arrive_expect_tx(q_full, 2 * L::Q_BYTES);
+      uint32_t kv = 0;  // key tiles loaded so far: ring position, running across items
+      bool ok = true;
+      int it = -1;
+      FOR_EACH_ITEM(item) {
+        if (!ok) break;
+        ++it;
+        const Item3 w = decode_item(p, item);
+        // Q of the previous item is no longer read once its last Q K^T has completed
+        if (it > 0 && !mbar_wait(q_empty, (it - 1) & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_PRODUCER)) {
+          ok = false;
+          break;
+        }
+        // Both query tiles; rows beyond the queries arrive as zeros (their results are never stored).
+        mbar_arrive_expect_tx(q_full, 2 * L::Q_BYTES);
 #pragma unroll
-      for (int t = 0; t < 2; ++t)
+        for (int t = 0; t < 2; ++t)
 #pragma unroll
-        for (int h = 0; h < HD / 64; ++h)
-          tma_load_4d(smem + L::Q_OFF + t * L::Q_BYTES + h * SUBTILE3, &tmQ, q_full, h * 64, q0 + t * BQ3, hq, b);
-      for (int j = 0; j < n_max; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1u;
-        if (!mbar_wait(&k_empty[st], ph ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_PRODUCER)) break;
-        mbar_arrive_expect_tx(&k_full[st], L::KV_BYTES);
+          for (int h = 0; h < HD / 64; ++h)
+            tma_load_4d(smem + L::Q_OFF + t * L::Q_BYTES + h * SUBTILE3, &tmQ, q_full, h * 64, w.q0 + t * BQ3, w.hq, w.b);
+        for (int j = 0; j < w.n_max; ++j, ++kv) {
+          const int st = kv & 1;
+          const uint32_t ph = (kv >> 1) & 1u;
+          if (!mbar_wait(&k_empty[st], ph ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&k_full[st], L::KV_BYTES);
 #pragma unroll
-        for (int h = 0; h < HD / 64; ++h)
-          tma_load_4d(smem + L::K_OFF + st * L::KV_BYTES + h * SUBTILE3, &tmK, &k_full[st], h * 64, j * BKV3, hkv, b);
-        if (!mbar_wait(&v_empty[st], ph ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_PRODUCER)) break;
-        mbar_arrive_expect_tx(&v_full[st], L::KV_BYTES);
+          for (int h = 0; h < HD / 64; ++h)
+            tma_load_4d(smem + L::K_OFF + st * L::KV_BYTES + h * SUBTILE3, &tmK, &k_full[st], h * 64, j * BKV3, w.hkv, w.b);
+          if (!mbar_wait(&v_empty[st], ph ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&v_full[st], L::KV_BYTES);
 #pragma unroll
-        for (int h = 0; h < HD / 64; ++h)
-          tma_load_4d(smem + L::V_OFF + st * L::KV_BYTES + h * SUBTILE3, &tmV, &v_full[st], h * 64, j * BKV3, hkv, b);
+          for (int h = 0; h < HD / 64; ++h)
+            tma_load_4d(smem + L::V_OFF + st * L::KV_BYTES + h * SUBTILE3, &tmV, &v_full[st], h * 64, j * BKV3, w.hkv, w.b);
+        }
       }
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (TV & 16) {
-      // The whole warp walks the schedule (waits included) and one elected lane issues: all
-      // descriptor arithmetic stays warp-uniform, and per MMA it is one 64-bit add of a
-      // compile-time constant to a descriptor built once per product.
-      constexpr uint32_t idesc_qk = make_idesc(UMMA_BF16, BQ3, BKV3, false, false);
-      constexpr uint32_t idesc_pv = make_idesc(UMMA_BF16, BQ3, HD, false, true);
-      const uint32_t q_addr = smem_u32(smem + L::Q_OFF);
-      const uint32_t k_addr = smem_u32(smem + L::K_OFF);
-      const uint32_t v_addr = smem_u32(smem + L::V_OFF);
-      auto issue_qk = [&](int t, int j) {
-        const uint64_t qd = make_smem_desc_sw128(q_addr + t * L::Q_BYTES, 16, 1024);
-        const uint64_t kd = make_smem_desc_sw128(k_addr + (j & 1) * L::KV_BYTES, 16, 1024);
-        const uint32_t d = tmem_base + S_COL + t * 128;
-        if (elect_one()) {
+    constexpr uint32_t idesc_qk = make_idesc(UMMA_BF16, BQ3, BKV3, false, false);
+    constexpr uint32_t idesc_pv = make_idesc(UMMA_BF16, BQ3, HD, false, true);
+    const uint32_t q_addr = smem_u32(smem + L::Q_OFF);
+    const uint32_t k_addr = smem_u32(smem + L::K_OFF);
+    const uint32_t v_addr = smem_u32(smem + L::V_OFF);
+    // S_t = Q_t K^T with K in ring stage `st`, into tile t's score columns
+    auto issue_qk = [&](int t, int st) {
+      const uint64_t qd = make_smem_desc_sw128(q_addr + t * L::Q_BYTES, 16, 1024);
+      const uint64_t kd = make_smem_desc_sw128(k_addr + st * L::KV_BYTES, 16, 1024);
+      const uint32_t d = tmem_base + S_COL + t * 128;
+      if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < HD / 16; ++k) {
-            constexpr int dummy = 0;
-            (void)dummy;
-            const uint64_t off = static_cast<uint64_t>(((k / 4) * SUBTILE3 + (k % 4) * 32) >> 4);  // address field counts 16-byte units
-            umma_f16_ss(d, qd + off, kd + off, idesc_qk, k != 0 ? 1u : 0u);
-          }
-          umma_commit(&s_full[t]);
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint64_t off = static_cast<uint64_t>(((k / 4) * SUBTILE3 + (k % 4) * 32) >> 4);  // the address field counts 16-byte units
+          umma_f16_ss(d, qd + off, kd + off, idesc_qk, k != 0 ? 1u : 0u);
         }
-        __syncwarp();
-      };
-      bool ok = wait_warp3(q_full, 0, abort_flag, p.dev_status, DEV_TIMEOUT_MMA);
-      if (ok && n_max > 0) {
-        ok = wait_warp3(&k_full[0], 0, abort_flag, p.dev_status, DEV_TIMEOUT_MMA);
-        if (ok) {
-          tc_fence_after_sync();
-          for (int t = 0; t < 2; ++t)
-            if (n_of(t) > 0) issue_qk(t, 0);
-          if (elect_one()) umma_commit(&k_empty[0]);
-          __syncwarp();
-        }
+        umma_commit(&s_full[t]);
       }
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1u;
-        const uint32_t tph = j & 1u;
-        const bool have_next = j + 1 < n_max;
-        if (!wait_warp3(&v_full[st], ph, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) break;
+      __syncwarp();
+    };
+    uint32_t kv = 0;            // key tiles consumed so far (ring position)
+    uint32_t cnt[2] = {0u, 0u};  // key tiles each query tile has been through: phase of its barriers
+    bool ok = true;
+    int it = -1;
+    FOR_EACH_ITEM(item) {
+      if (!ok) break;
+      ++it;
+      const Item3 w = decode_item(p, item);
+      auto n_of = [&](int t) { return t == 0 ? w.n_a : w.n_b; };
+      if (!wait_warp3(q_full, it & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_MMA) ||
+          !wait_warp3(&k_full[kv & 1], (kv >> 1) & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      // The item's first scores overwrite the columns the previous item's last P V reads P from;
+      // the tensor core runs one thread's MMAs in issue order.
+      for (int t = 0; t < 2; ++t)
+        if (n_of(t) > 0) issue_qk(t, kv & 1);
+      if (elect_one()) {
+        umma_commit(&k_empty[kv & 1]);
+        if (w.n_max == 1) umma_commit(q_empty);
+      }
+      __syncwarp();
+      for (int j = 0; j < w.n_max && ok; ++j, ++kv) {
+        const int st = kv & 1;
+        const bool have_next = j + 1 < w.n_max;
+        if (!wait_warp3(&v_full[st], (kv >> 1) & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
         bool next_k_seen = false;
         const uint64_t vd = make_smem_desc_sw128(v_addr + st * L::KV_BYTES, SUBTILE3, 1024);
-        for (int t = 0; t < 2 && ok; ++t) {
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (!ok) break;
           if (j < n_of(t)) {
-            if (lane == 0) DBG_MARK(j, t * 4 + 0);
+            // O_t += P_t V_j, P_t read from tensor memory, its first 64 keys consumed while the
+            // softmax warps still produce the rest. (The first product of an item overwrites
+            // O_t: the softmax warps hand over P only after they have read the previous item's
+            // result out of it.)
             const uint32_t od = tmem_base + O_COL + t * 128, pa = tmem_base + S_COL + t * 128;
+            const uint32_t tph = (cnt[t] + j) & 1u;
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
               if (!wait_warp3(&p_half[2 * t + hf], tph, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
@@ -244,275 +299,182 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               tc_fence_after_sync();
               if (elect_one()) {
 #pragma unroll
-                for (int k = hf * 4; k < hf * 4 + 4; ++k)
+                for (int k = hf * 4; k < hf * 4 + 4; ++k)  // 16 keys of P = 8 packed columns; V rows are keys, 2048 bytes per 16 keys and 64 head-dim elements
                   umma_f16_ts(od, pa + k * 8, vd + static_cast<uint64_t>((k * 2048) >> 4), idesc_pv, (j | k) != 0 ? 1u : 0u);
                 if (hf == 1) umma_commit(&pv_done[t]);
               }
               __syncwarp();
             }
             if (!ok) break;
-            if (lane == 0) DBG_MARK(j, t * 4 + 1);
           }
           if (j + 1 < n_of(t)) {
+            // The next scores of this tile overwrite the columns the product just issued reads P from.
             if (!next_k_seen) {
-              if (!wait_warp3(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
+              if (!wait_warp3(&k_full[(kv + 1) & 1], ((kv + 1) >> 1) & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
                 ok = false;
                 break;
               }
               tc_fence_after_sync();
               next_k_seen = true;
             }
-            issue_qk(t, j + 1);
-            if (lane == 0) DBG_MARK(j, t * 4 + 2);
+            issue_qk(t, (kv + 1) & 1);
           }
         }
         if (!ok) break;
         if (elect_one()) {
-          umma_commit(&v_empty[st]);
-          if (have_next) umma_commit(&k_empty[(j + 1) & 1]);
+          umma_commit(&v_empty[st]);                           // both tiles' P V of this stage are issued
+          if (have_next) umma_commit(&k_empty[(kv + 1) & 1]);  // and both tiles' Q K^T on the next K
+          if (j + 2 == w.n_max) umma_commit(q_empty);          // those were the item's last Q K^T
         }
         __syncwarp();
       }
-    } else if (lane == 0) {
-      constexpr uint32_t idesc_qk = make_idesc(UMMA_BF16, BQ3, BKV3, false, false);
-      constexpr uint32_t idesc_pv = make_idesc(UMMA_BF16, BQ3, HD, false, true);
-      const uint32_t q_addr = smem_u32(smem + L::Q_OFF);
-      const uint32_t k_addr = smem_u32(smem + L::K_OFF);
-      const uint32_t v_addr = smem_u32(smem + L::V_OFF);
-      // S_t = Q_t K_j^T into tile t's score columns
-      auto issue_qk = [&](int t, int j) {
-        const uint32_t qa = q_addr + t * L::Q_BYTES, ka = k_addr + (j & 1) * L::KV_BYTES;
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t off = (k / 4) * SUBTILE3 + (k % 4) * 32;
-          umma_f16_ss(tmem_base + S_COL + t * 128, make_smem_desc_sw128(qa + off, 16, 1024), make_smem_desc_sw128(ka + off, 16, 1024), idesc_qk,
-                      k != 0 ? 1u : 0u);
-        }
-        umma_commit(&s_full[t]);
-      };
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.dev_status, DEV_TIMEOUT_MMA);
-      if (ok && n_max > 0) {
-        ok = mbar_wait(&k_full[0], 0, abort_flag, p.dev_status, DEV_TIMEOUT_MMA);
-        if (ok) {
-          tc_fence_after_sync();
-          for (int t = 0; t < 2; ++t)
-            if (n_of(t) > 0) issue_qk(t, 0);
-          umma_commit(&k_empty[0]);
-        }
-      }
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1u;   // phase of the K / V stage
-        const uint32_t tph = j & 1u;         // phase of the per-tile barriers
-        const bool have_next = j + 1 < n_max;
-        if (!mbar_wait(&v_full[st], ph, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) break;
-        bool next_k_seen = false;
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (j < n_of(t)) {
-            // O_t += P_t V_j, P_t read from tensor memory, its first 64 keys consumed while the
-            // softmax warps still produce the rest
-            const uint32_t va = v_addr + st * L::KV_BYTES;
-            DBG_MARK(j, t * 4 + 0);
-#pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-              if (!mbar_wait(&p_half[2 * t + hf], tph, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
-                ok = false;
-                break;
-              }
-              tc_fence_after_sync();
-#pragma unroll
-              for (int k = hf * 4; k < hf * 4 + 4; ++k) {
-                // 16 keys of P = 8 packed columns; V rows are keys, 64 head-dim elements per 128-byte row
-                umma_f16_ts(tmem_base + O_COL + t * 128, tmem_base + S_COL + t * 128 + k * 8, make_smem_desc_sw128(va + k * 2048, SUBTILE3, 1024),
-                            idesc_pv, (j | k) != 0 ? 1u : 0u);
-              }
-            }
-            if (!ok) break;
-            umma_commit(&pv_done[t]);
-            DBG_MARK(j, t * 4 + 1);
-          }
-          if (j + 1 < n_of(t)) {
-            // The next scores of this tile overwrite the columns the product just issued reads P
-            // from; the tensor core runs this thread's MMAs in issue order.
-            if (!next_k_seen) {
-              if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
-                ok = false;
-                break;
-              }
-              tc_fence_after_sync();
-              next_k_seen = true;
-            }
-            issue_qk(t, j + 1);
-            DBG_MARK(j, t * 4 + 2);
-          }
-        }
-        if (!ok) break;
-        umma_commit(&v_empty[st]);                          // both tiles' P V of this stage are issued
-        if (have_next) umma_commit(&k_empty[(j + 1) & 1]);  // and both tiles' Q K^T on the next K
-      }
+      cnt[0] += w.n_a;
+      cnt[1] += w.n_b;
     }
   } else {
     // ---------------------------------------------------------------- softmax
     const int t = (warp - 2) >> 2;  // which query tile this warp group serves
     const int quarter = warp & 3;   // tensor-memory lanes [32 quarter, +32) are this warp's
     const int row = quarter * 32 + lane;
-    const int q0t = q0 + t * BQ3;
-    const int q_row = q0t + row;
-    const int n_mine = n_of(t);
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_addr = tmem_base + S_COL + t * 128 + lane_off;
     const uint32_t o_addr = tmem_base + O_COL + t * 128 + lane_off;
     uint64_t* my_s_full = &s_full[t];
     uint64_t* my_p_half = &p_half[2 * t];
-    float m_used = -INFINITY;
-    float l = 0.f;
+    uint32_t cnt = 0;  // key tiles this query tile has been through over all items
     bool ok = true;
-    for (int j = 0; j < n_mine; ++j) {
-      if (!wait_warp3(my_s_full, j & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_SOFTMAX)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      if (row == 0) DBG_MARK(j, 8 + t * 4 + 0);
-      const int col0 = j * BKV3;
-      const bool need_mask = (col0 + BKV3 > p.Skv) || (p.causal && (col0 + BKV3 - 1 > q0t + offset));
-      const int limit = need_mask ? (p.causal ? min(p.Skv - 1, q_row + offset) : (p.Skv - 1)) - col0 : BKV3;  // last visible column in this tile
-      // pass 1: row max of the scores, two 32-column loads in flight at a time
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;  // independent chains
-      uint32_t sr[(TV & 4) ? 128 : 1];  // TV bit 2: the whole row of scores
-      if (TV & 4) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[(TV & 4) ? c * 32 : 0]));
-        tmem_ld_wait();
-        if (need_mask) {
-#pragma unroll
-          for (int i = 0; i < ((TV & 4) ? 128 : 1); ++i)
-            if (i > limit) sr[i] = 0xff800000u;
+    FOR_EACH_ITEM(item) {
+      if (!ok) break;
+      const Item3 w = decode_item(p, item);
+      const int n_mine = t == 0 ? w.n_a : w.n_b;
+      const int q0t = w.q0 + t * BQ3;
+      const int q_row = q0t + row;
+      float m_used = -INFINITY;
+      float l = 0.f;
+      for (int j = 0; j < n_mine; ++j) {
+        if (!wait_warp3(my_s_full, (cnt + j) & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_SOFTMAX)) {
+          ok = false;
+          break;
         }
+        tc_fence_after_sync();
+        const int col0 = j * BKV3;
+        const bool need_mask = (col0 + BKV3 > p.Skv) || (p.causal && (col0 + BKV3 - 1 > q0t + offset));
+        const int limit = need_mask ? (p.causal ? min(p.Skv - 1, q_row + offset) : (p.Skv - 1)) - col0 : BKV3;  // last visible column in this tile
+        // pass 1: row max of the scores, two 32-column loads in flight at a time
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;  // independent chains
 #pragma unroll
-        for (int i = 0; i < ((TV & 4) ? 128 : 1); i += 8) {
-          mx0 = fmax3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
-          mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
-          mx2 = fmax3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
-          mx3 = fmax3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
-        }
-      } else if (TV & 1) {
-        mx0 = 0.f;
-      } else
+        for (int c = 0; c < 4; c += 2) {
+          uint32_t s0[32], s1[32];
+          tmem_ld_32x32b_x32(s_addr + c * 32, s0);
+          tmem_ld_32x32b_x32(s_addr + c * 32 + 32, s1);
+          tmem_ld_wait();
+          if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < 4; c += 2) {
-        uint32_t s0[32], s1[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, s0);
-        tmem_ld_32x32b_x32(s_addr + c * 32 + 32, s1);
-        tmem_ld_wait();
-        if (need_mask) {
+            for (int i = 0; i < 32; ++i) {
+              if (c * 32 + i > limit) s0[i] = 0xff800000u;  // -inf
+              if (c * 32 + 32 + i > limit) s1[i] = 0xff800000u;
+            }
+          }
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (c * 32 + i > limit) s0[i] = 0xff800000u;  // -inf
-            if (c * 32 + 32 + i > limit) s1[i] = 0xff800000u;
+          for (int i = 0; i < 32; i += 4) {
+            mx0 = fmax3(mx0, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+            mx1 = fmax3(mx1, __uint_as_float(s0[i + 2]), __uint_as_float(s0[i + 3]));
+            mx2 = fmax3(mx2, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+            mx3 = fmax3(mx3, __uint_as_float(s1[i + 2]), __uint_as_float(s1[i + 3]));
           }
         }
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          mx0 = fmax3(mx0, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
-          mx1 = fmax3(mx1, __uint_as_float(s0[i + 2]), __uint_as_float(s0[i + 3]));
-          mx2 = fmax3(mx2, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
-          mx3 = fmax3(mx3, __uint_as_float(s1[i + 2]), __uint_as_float(s1[i + 3]));
+        float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        mx *= p.scale_log2;  // scale > 0: max commutes with the scaling
+        // lazy rescale: move the reference max only when it grew by more than 8 (2^8 headroom)
+        float alpha = 1.f;
+        const bool need = (mx > m_used + 8.f) || (m_used == -INFINITY && mx > -INFINITY);
+        if (need) {
+          alpha = (m_used == -INFINITY) ? 0.f : ex2_approx(m_used - mx);
+          m_used = mx;
         }
+        const bool warp_need = __any_sync(0xffffffffu, need);
+        if (j > 0 && warp_need) {
+          // s_full(j) fired after every MMA issued before it, this tile's P V of key tile j - 1
+          // included: the accumulator is up to date and nothing writes it until P(j) is handed over
+#pragma unroll
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(o_addr + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32b_x32(o_addr + c * 32, o);
+          }
+        }
+        // pass 2: P = exp2(scale*S - m), row sum, bf16 pairs written over the S columns; each
+        // half (64 keys) is handed to the MMA warp as soon as it is in tensor memory
+        const float msub = (m_used == -INFINITY) ? 0.f : m_used;
+        float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t s0[32], s1[32];
+          tmem_ld_32x32b_x32(s_addr + hf * 64, s0);
+          tmem_ld_32x32b_x32(s_addr + hf * 64 + 32, s1);
+          tmem_ld_wait();
+          uint32_t pk[32];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float p0 = ex2_approx(fmaf(__uint_as_float(s0[2 * i]), p.scale_log2, -msub));
+            float p1 = ex2_approx(fmaf(__uint_as_float(s0[2 * i + 1]), p.scale_log2, -msub));
+            float p2 = ex2_approx(fmaf(__uint_as_float(s1[2 * i]), p.scale_log2, -msub));
+            float p3 = ex2_approx(fmaf(__uint_as_float(s1[2 * i + 1]), p.scale_log2, -msub));
+            if (need_mask) {
+              const int cbase = hf * 64 + 2 * i;
+              p0 = (cbase <= limit) ? p0 : 0.f;
+              p1 = (cbase + 1 <= limit) ? p1 : 0.f;
+              p2 = (cbase + 32 <= limit) ? p2 : 0.f;
+              p3 = (cbase + 33 <= limit) ? p3 : 0.f;
+            }
+            rs0 += p0;
+            rs1 += p1;
+            rs2 += p2;
+            rs3 += p3;
+            pk[i] = pack_bf16x2(p0, p1);
+            pk[16 + i] = pack_bf16x2(p2, p3);
+          }
+          tmem_st_32x32b_x32(s_addr + hf * 32, pk);
+          tmem_st_wait();
+          tc_fence_before_sync();
+          mbar_arrive(&my_p_half[hf]);
+        }
+        l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
       }
-      if (row == 0) DBG_MARK(j, 8 + t * 4 + 1);
-      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      mx *= p.scale_log2;  // scale > 0: max commutes with the scaling
-      // lazy rescale: move the reference max only when it grew by more than 8 (2^8 headroom)
-      float alpha = 1.f;
-      const bool need = (mx > m_used + 8.f) || (m_used == -INFINITY && mx > -INFINITY);
-      if (need) {
-        alpha = (m_used == -INFINITY) ? 0.f : ex2_approx(m_used - mx);
-        m_used = mx;
-      }
-      const bool warp_need = __any_sync(0xffffffffu, need);
-      if (j > 0 && warp_need) {
-        // s_full(j) fired after every MMA issued before it, this tile's P V of key tile j - 1
-        // included: the accumulator is up to date and nothing writes it until P(j) is handed over
+      if (!ok) break;
+      if (n_mine > 0) {
+        // O_t is final once this tile's last P V has completed. Its columns are read out here
+        // before these threads hand over the next item's first P, which is what the MMA warp
+        // waits for before it overwrites them.
+        if (!wait_warp3(&pv_done[t], (cnt + n_mine - 1) & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_SOFTMAX)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+        char* obase = static_cast<char*>(p.O);
+        const int64_t oidx = static_cast<int64_t>(w.b) * p.sob + static_cast<int64_t>(w.hq) * p.soh + static_cast<int64_t>(q_row) * p.sos;
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t o[32];
           tmem_ld_32x32b_x32(o_addr + c * 32, o);
           tmem_ld_wait();
+          if (q_row < p.Sq) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_32x32b_x32(o_addr + c * 32, o);
-        }
-      }
-      // pass 2: P = exp2(scale*S - m), row sum, bf16 pairs written over the S columns; each
-      // half (64 keys) is handed to the MMA warp as soon as it is in tensor memory
-      const float msub = (m_used == -INFINITY) ? 0.f : m_used;
-      float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+            for (int g = 0; g < 4; ++g) {
+              float v[8];
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t s0l[(TV & 4) ? 1 : 32], s1l[(TV & 4) ? 1 : 32];
-        if (!(TV & 4)) {
-          tmem_ld_32x32b_x32(s_addr + hf * 64, *reinterpret_cast<uint32_t(*)[32]>(&s0l[0]));
-          tmem_ld_32x32b_x32(s_addr + hf * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&s1l[0]));
-          tmem_ld_wait();
-        }
-        const uint32_t* s0 = (TV & 4) ? &sr[(TV & 4) ? hf * 64 : 0] : s0l;
-        const uint32_t* s1 = (TV & 4) ? &sr[(TV & 4) ? hf * 64 + 32 : 0] : s1l;
-        uint32_t pk[32];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p0 = fmaf(__uint_as_float(s0[2 * i]), p.scale_log2, -msub);
-          float p1 = fmaf(__uint_as_float(s0[2 * i + 1]), p.scale_log2, -msub);
-          float p2 = fmaf(__uint_as_float(s1[2 * i]), p.scale_log2, -msub);
-          float p3 = fmaf(__uint_as_float(s1[2 * i + 1]), p.scale_log2, -msub);
-          if (!(TV & 2)) {
-            p0 = ex2_approx(p0);
-            p1 = ex2_approx(p1);
-            p2 = ex2_approx(p2);
-            p3 = ex2_approx(p3);
+              for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(o[g * 8 + i]) * inv_l;
+              store8_from_f32(obase, p.o_dtype, oidx + c * 32 + g * 8, v);
+            }
           }
-          if (need_mask) {
-            const int cbase = hf * 64 + 2 * i;
-            p0 = (cbase <= limit) ? p0 : 0.f;
-            p1 = (cbase + 1 <= limit) ? p1 : 0.f;
-            p2 = (cbase + 32 <= limit) ? p2 : 0.f;
-            p3 = (cbase + 33 <= limit) ? p3 : 0.f;
-          }
-          rs0 += p0;
-          rs1 += p1;
-          rs2 += p2;
-          rs3 += p3;
-          pk[i] = pack_bf16x2(p0, p1);
-          pk[16 + i] = pack_bf16x2(p2, p3);
         }
-        tmem_st_32x32b_x32(s_addr + hf * 32, pk);
-        tmem_st_wait();
         tc_fence_before_sync();
-        mbar_arrive(&my_p_half[hf]);
-        if (row == 0) DBG_MARK(j, 8 + t * 4 + 2 + hf);
       }
-      l = l * alpha + ((rs0 + rs1) + (rs2 + rs3));
-    }
-    if (ok && n_mine > 0 && wait_warp3(&pv_done[t], (n_mine - 1) & 1u, abort_flag, p.dev_status, DEV_TIMEOUT_SOFTMAX)) {
-      tc_fence_after_sync();
-      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-      char* obase = static_cast<char*>(p.O);
-      const int64_t oidx = static_cast<int64_t>(b) * p.sob + static_cast<int64_t>(hq) * p.soh + static_cast<int64_t>(q_row) * p.sos;
-#pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t o[32];
-        tmem_ld_32x32b_x32(o_addr + c * 32, o);
-        tmem_ld_wait();
-        if (q_row < p.Sq) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(o[g * 8 + i]) * inv_l;
-            store8_from_f32(obase, p.o_dtype, oidx + c * 32 + g * 8, v);
-          }
-        }
-      }
+      cnt += n_mine;
     }
   }
 
@@ -530,7 +492,7 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 }
 
-template <int HD, int TV>
+template <int HD>
 int launch3_hd(lh_ctx* ctx, const AttnProblem& a) {
   using L = Attn3Smem<HD>;
   CUtensorMap tmQ, tmK, tmV;
@@ -556,39 +518,14 @@ int launch3_hd(lh_ctx* ctx, const AttnProblem& a) {
   p.scale_log2 = a.scale * 1.44269504088896340736f;
   p.causal = a.causal;
   p.num_q_pairs = (a.Sq + 2 * BQ3 - 1) / (2 * BQ3);
+  const int64_t items = static_cast<int64_t>(a.B) * a.Hq * p.num_q_pairs;
+  p.num_items = static_cast<int>(items);
   p.dev_status = ctx->dev_status;
-  p.dbg = nullptr;
-  p.dbg_block = 0;
-  static const int dbg_on = getenv("LH_ATTN_DBG") ? atoi(getenv("LH_ATTN_DBG")) : -1;
-  static long long* dbg_buf = nullptr;
-  if (dbg_on >= 0) {
-    if (!dbg_buf) cudaMalloc(&dbg_buf, 12 * 16 * sizeof(long long));
-    cudaMemsetAsync(dbg_buf, 0, 12 * 16 * sizeof(long long), ctx->stream);
-    p.dbg = dbg_buf;
-    p.dbg_block = dbg_on;
-  }
-  auto kernel = attn_fwd_tc3_kernel<HD, TV>;
+  auto kernel = attn_fwd_tc3_kernel<HD>;
   LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
-  const int64_t grid = static_cast<int64_t>(a.B) * a.Hq * p.num_q_pairs;
+  const int grid = items < ctx->sm_count ? static_cast<int>(items) : ctx->sm_count;  // one persistent CTA per SM
   kernel<<<static_cast<unsigned>(grid), ATT3_THREADS, L::DYN_BYTES, ctx->stream>>>(tmQ, tmK, tmV, p);
   LH_CHECK_LAUNCH(ctx, "attn_fwd_tc3_kernel");
-  if (dbg_on >= 0) {
-    static int printed = 0;
-    long long h[12 * 16];
-    cudaStreamSynchronize(ctx->stream);
-    cudaMemcpy(h, dbg_buf, sizeof(h), cudaMemcpyDeviceToHost);
-    if (printed++ == 3) {
-      long long t0 = 0;
-      for (int i = 0; i < 12 * 16; ++i)
-        if (h[i] && (!t0 || h[i] < t0)) t0 = h[i];
-      fprintf(stderr, "attn timeline (clk from first mark): per j: MMA A[pv_wait pv_issued qk_issued -] B[...] | softmax A[s_full pass1 half0 half1] B[...]\n");
-      for (int j = 0; j < 12; ++j) {
-        fprintf(stderr, "j=%2d:", j);
-        for (int k = 0; k < 16; ++k) fprintf(stderr, " %6lld%s", h[j * 16 + k] ? h[j * 16 + k] - t0 : -1, (k % 4 == 3) ? " |" : "");
-        fprintf(stderr, "\n");
-      }
-    }
-  }
   return LH_OK;
 }
 
@@ -596,20 +533,8 @@ int launch3_hd(lh_ctx* ctx, const AttnProblem& a) {
 
 int attn_tc3_launch(lh_ctx* ctx, const AttnProblem& a) {
   if (a.scale <= 0.f) return set_error(ctx, LH_ERR_UNSUPPORTED, "attention: scale must be positive");
-  static const int tv = getenv("LH_ATTN_TEST") ? atoi(getenv("LH_ATTN_TEST")) : 0;  // experiment switch (development only)
-  if (a.D == 128) {
-    switch (tv) {
-      case 1: return launch3_hd<128, 1>(ctx, a);
-      case 2: return launch3_hd<128, 2>(ctx, a);
-      case 3: return launch3_hd<128, 3>(ctx, a);
-      case 4: return launch3_hd<128, 4>(ctx, a);
-      case 6: return launch3_hd<128, 6>(ctx, a);
-      case 16: return launch3_hd<128, 16>(ctx, a);
-      case 19: return launch3_hd<128, 19>(ctx, a);
-      default: return launch3_hd<128, 0>(ctx, a);
-    }
-  }
-  return launch3_hd<64, 0>(ctx, a);
+  if (a.D == 128) return launch3_hd<128>(ctx, a);
+  return launch3_hd<64>(ctx, a);
 }
 
 // What the tensor-core kernels take: bf16 Q / K / V with unit stride in the head dimension,
@@ -636,8 +561,7 @@ int attn_tc_supported(const lh_ctx* ctx, const AttnProblem& a) {
 int attn_tc_launch(lh_ctx* ctx, const AttnProblem& a) {
   // One query tile per (batch, head): nothing to ping-pong with, two independent blocks per SM
   // serve such problems better.
-  static const int pick = getenv("LH_ATTN_KERNEL") ? atoi(getenv("LH_ATTN_KERNEL")) : 0;  // experiment switch (development only)
-  if (pick == 2 || (pick == 0 && a.Sq <= BQ3)) return attn_tc2_launch(ctx, a);
+  if (a.Sq <= BQ3) return attn_tc2_launch(ctx, a);
   return attn_tc3_launch(ctx, a);
 }
 

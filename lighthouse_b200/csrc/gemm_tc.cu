@@ -39,6 +39,7 @@ struct GemmTcParams {
   int n_out;  // columns of D (N, or N/2 with the SwiGLU epilogue)
   int num_m_blocks, num_n_blocks, num_k_blocks;
   int group_m;  // row-blocks per rasterisation group
+  int seg_k_blocks;  // SEGS > 1: k-blocks per accumulator
   EpiParams epi;
   int* dev_status;
 };
@@ -163,12 +164,17 @@ __device__ __forceinline__ void load_row_segment(uint4 (&seg)[8], const void* ba
 // TF32: the operands are f32 arrays read as tf32 (kind::tf32, K = 8 per instruction, 32
 // elements per 128-byte swizzle row); everything else - ring, tensor memory, epilogue - is the
 // bf16 kernel's.
-template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, bool TF32 = false>
+// SEGS > 1 (the 3 x TF32 path): the k range is cut into up to SEGS segments, each summed
+// in its own accumulator (SEGS * BN columns of tensor memory, no double buffering across tiles)
+// and the segments' sums are added with correctly rounded f32 adds in the epilogue: the tensor
+// core adds into an accumulator with truncation, which biases long sums.
+template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, bool TF32 = false, int SEGS = 1>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmD, const GemmTcParams p) {
   using L = SmemLayout<BN, STAGES>;
-  constexpr int TMEM_COLS = tmem_cols_for(BN);
+  constexpr int TMEM_COLS = SEGS > 1 ? tmem_cols_for((SEGS * BN + 1) / 2) : tmem_cols_for(BN);
+  static_assert(SEGS == 1 || (TF32 && SEGS * BN <= 512), "segmented accumulation is the tf32 path's");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 
@@ -250,12 +256,14 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool ok = true;
       int t = 0;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
-        const int buf = t & 1;
-        const uint32_t acc_phase = (t >> 1) & 1u;
+        const int buf = SEGS > 1 ? 0 : (t & 1);
+        const uint32_t acc_phase = SEGS > 1 ? (t & 1u) : ((t >> 1) & 1u);
         if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) break;
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          const int seg = SEGS > 1 ? kb / p.seg_k_blocks : 0;
+          const int kb_in_seg = SEGS > 1 ? kb - seg * p.seg_k_blocks : kb;
+          const uint32_t d_tmem = tmem_base + (SEGS > 1 ? seg : buf) * BN;
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
             ok = false;
             break;
@@ -268,8 +276,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint64_t adesc = make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
             const uint64_t bdesc = B_KMAJOR ? make_smem_desc_sw128(b_addr + k * 32, 16, 1024)
                                             : make_smem_desc_sw128(b_addr + k * 2048, 64 * BK * 2, 1024);
-            if (TF32) umma_tf32_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
-            else umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (TF32) umma_tf32_ss(d_tmem, adesc, bdesc, idesc, (kb_in_seg | k) != 0 ? 1u : 0u);
+            else umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb_in_seg | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == STAGES) {
@@ -290,8 +298,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       int m_blk, n_blk;
       tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, m_blk, n_blk);
-      const int buf = t & 1;
-      const uint32_t acc_phase = (t >> 1) & 1u;
+      const int buf = SEGS > 1 ? 0 : (t & 1);
+      const uint32_t acc_phase = SEGS > 1 ? (t & 1u) : ((t >> 1) & 1u);
+      const int nseg = SEGS > 1 ? (p.num_k_blocks + p.seg_k_blocks - 1) / p.seg_k_blocks : 1;
       if (!mbar_wait_warp(&tmem_full[buf], acc_phase, abort_flag, p.dev_status, DEV_TIMEOUT_EPILOGUE, lane))
         break;
       tc_fence_after_sync();
@@ -347,6 +356,19 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < CHUNK; ++i) v[i] = __uint_as_float(raw[i]);
+          if (SEGS > 1) {
+            // the later segments' sums, added one by one with rounded f32 adds
+            for (int sg = 1; sg < nseg; ++sg) {
+#pragma unroll
+              for (int h = 0; h < CHUNK / 32; ++h) {
+                uint32_t(&part)[32] = *reinterpret_cast<uint32_t(*)[32]>(&raw[h * 32]);
+                tmem_ld_32x32b_x32(taddr + sg * BN + u * CHUNK + h * 32, part);
+              }
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < CHUNK; ++i) v[i] += __uint_as_float(raw[i]);
+            }
+          }
         } else {
           // B columns of this tile are [gate (BN/2) | up (BN/2)]: D = silu(gate) * up.
 #pragma unroll
@@ -442,8 +464,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
-template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, bool TF32 = false>
-int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi) {
+template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, bool TF32 = false, int SEGS = 1>
+int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int seg_k_blocks = 0) {
   using L = SmemLayout<BN, STAGES>;
   CUtensorMap tmA, tmB, tmD;
   const int n_out = epi.swiglu ? pr.N / 2 : pr.N;
@@ -495,8 +517,9 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi) {
     while (p.group_m < 64 && 2 * static_cast<size_t>(p.group_m) * row_block_bytes <= GROUP_A_PANEL_BYTES && p.num_m_blocks > p.group_m) p.group_m *= 2;
   }
   p.epi = epi;
+  p.seg_k_blocks = seg_k_blocks > 0 ? seg_k_blocks : p.num_k_blocks;
   p.dev_status = ctx->dev_status;
-  auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES, OUT_F32, TF32>;
+  auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES, OUT_F32, TF32, SEGS>;
   LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
   // A persistent grid that fills the GPU would make side-stream kernels (collectives) wait for
@@ -612,25 +635,35 @@ int gemm_tc_bf16_launch(lh_ctx* ctx, const GemmProblem& p) {
 // per segment.
 namespace {
 
-__global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict__ src, int64_t s_row, int64_t s_k, int rows, int K,
-                                                         float* __restrict__ dst, int64_t ld, int lo_slot, int seg) {
+struct SplitOperand {
+  const float* src;
+  int64_t s_row, s_k;
+  int rows;
+  float* dst;
+  int lo_slot;  // which of a segment's three slots takes the remainder (the other two take the head)
+};
+
+// Both operands in one launch: blockIdx.z selects A or B.
+__global__ void __launch_bounds__(256) split_tf32_kernel(const SplitOperand oa, const SplitOperand ob, int K, int64_t ld, int seg) {
   // 32 rows x 32 k per block through shared memory, so that both the read (along whichever of
   // row / k is contiguous in src) and the write (along k) are coalesced.
   __shared__ float tile[32][33];
+  const SplitOperand& o = blockIdx.z == 0 ? oa : ob;
   const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+  if (r0 >= o.rows) return;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
-  const bool k_contig = (s_k == 1);
+  const bool k_contig = (o.s_k == 1);
   for (int i = ty; i < 32; i += 8) {
     const int r = k_contig ? r0 + i : r0 + tx;
     const int k = k_contig ? k0 + tx : k0 + i;
-    const float v = (r < rows && k < K) ? src[r * s_row + k * s_k] : 0.f;
+    const float v = (r < o.rows && k < K) ? o.src[r * o.s_row + k * o.s_k] : 0.f;
     if (k_contig) tile[i][tx] = v;
     else tile[tx][i] = v;
   }
   __syncthreads();
   for (int i = ty; i < 32; i += 8) {
     const int r = r0 + i, k = k0 + tx;
-    if (r < rows && k < K) {
+    if (r < o.rows && k < K) {
       const float x = tile[i][tx];
       const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
       const float lo = x - hi;
@@ -638,10 +671,10 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict
       // three slots of len; the remainder sits in slot lo_slot, the head in the other two
       const int first = (k / seg) * seg;
       const int len = min(seg, K - first);
-      float* out = dst + r * ld + 3 * static_cast<int64_t>(first) + (k - first);
-      out[0] = lo_slot == 0 ? lo : hi;
-      out[len] = lo_slot == 1 ? lo : hi;
-      out[2 * len] = lo_slot == 2 ? lo : hi;
+      float* out = o.dst + r * ld + 3 * static_cast<int64_t>(first) + (k - first);
+      out[0] = o.lo_slot == 0 ? lo : hi;
+      out[len] = o.lo_slot == 1 ? lo : hi;
+      out[2 * len] = o.lo_slot == 2 ? lo : hi;
     }
   }
 }
@@ -686,28 +719,41 @@ int gemm_tc_tf32x3_launch(lh_ctx* ctx, const GemmProblem& p) {
   if (rc) return rc;
   float* a3 = static_cast<float*>(ctx->scratch);
   float* b3 = reinterpret_cast<float*>(static_cast<char*>(ctx->scratch) + a_pad);
-  const dim3 ga((p.K + 31) / 32, (p.M + 31) / 32), gb((p.K + 31) / 32, (p.N + 31) / 32);
-  split_tf32_kernel<<<ga, 256, 0, ctx->stream>>>(static_cast<const float*>(p.A), p.sam, p.sak, p.M, p.K, a3, ld, 1, TF32X3_SEGMENT);
-  LH_CHECK_LAUNCH(ctx, "split_tf32_kernel");
-  split_tf32_kernel<<<gb, 256, 0, ctx->stream>>>(static_cast<const float*>(p.B), p.sbn, p.sbk, p.N, p.K, b3, ld, 2, TF32X3_SEGMENT);
-  LH_CHECK_LAUNCH(ctx, "split_tf32_kernel");
-  // tile width by the same wave model as the bf16 kernel, between the two instantiated widths
+  {
+    const SplitOperand oa{static_cast<const float*>(p.A), p.sam, p.sak, p.M, a3, 1};
+    const SplitOperand ob{static_cast<const float*>(p.B), p.sbn, p.sbk, p.N, b3, 2};
+    const int max_rows = p.M > p.N ? p.M : p.N;
+    const dim3 grid((p.K + 31) / 32, (max_rows + 31) / 32, 2);
+    split_tf32_kernel<<<grid, 256, 0, ctx->stream>>>(oa, ob, p.K, ld, TF32X3_SEGMENT);
+    LH_CHECK_LAUNCH(ctx, "split_tf32_kernel");
+  }
   const int sms = ctx->sm_count - ctx->reserved_sms > 0 ? ctx->sm_count - ctx->reserved_sms : 1;
   const int64_t num_m = (p.M + BM - 1) / BM;
-  const int64_t w256 = (num_m * ((p.N + 255) / 256) + sms - 1) / sms, w128 = (num_m * ((p.N + 127) / 128) + sms - 1) / sms;
-  const bool wide = w256 * 256 <= w128 * 128 / 0.72;
+  const int64_t tiles256 = num_m * ((p.N + 255) / 256), tiles128 = num_m * ((p.N + 127) / 128);
   const int nseg = (p.K + TF32X3_SEGMENT - 1) / TF32X3_SEGMENT;
-  for (int sgm = 0; sgm < nseg; ++sgm) {
-    const int first = sgm * TF32X3_SEGMENT;
-    const int len = p.K - first < TF32X3_SEGMENT ? p.K - first : TF32X3_SEGMENT;
-    const bool is_first = sgm == 0, is_last = sgm == nseg - 1;
+  // Small and medium products: 64- or 128-wide tiles (whichever still gives every SM a tile)
+  // with four segment accumulators each, so a whole k range of 1024 is ONE launch (launch
+  // latency is what such products cost). Large ones: the wider tile's efficiency matters more
+  // than the launch count: two segments per launch.
+  // The caller's tile hint (bits 8-15 of the flags) overrides the choice below.
+  const int hint = static_cast<int>((p.flags >> 8) & 0xffu) * 8;
+  const int bn = (hint == 64 || hint == 128 || hint == 256) ? hint
+                 : tiles256 >= 2 * static_cast<int64_t>(sms) ? 256
+                 : tiles128 >= sms ? 128 : 64;
+  const bool wide = bn == 256;
+  const int per_launch = wide ? 2 : 4;
+  for (int s0 = 0; s0 < nseg; s0 += per_launch) {
+    const int s1 = s0 + per_launch < nseg ? s0 + per_launch : nseg;
+    const int first = s0 * TF32X3_SEGMENT;
+    const int last_k = s1 * TF32X3_SEGMENT < p.K ? s1 * TF32X3_SEGMENT : p.K;
+    const bool is_first = s0 == 0, is_last = s1 == nseg;
     GemmProblem q = p;
-    q.K = 3 * len;
+    q.K = 3 * (last_k - first);
     q.A = a3 + 3 * static_cast<int64_t>(first); q.sam = ld; q.sak = 1;
     q.B = b3 + 3 * static_cast<int64_t>(first); q.sbn = ld; q.sbk = 1;
     EpiParams epi;
     epi.D = p.D; epi.d_dtype = p.d_dtype; epi.ldd = p.sdm;
-    // the caller's C enters with the first segment, the running sum (D) with the later ones;
+    // the caller's C enters with the first launch, the running sum (D) with the later ones;
     // bias, activation and residual belong to the last
     epi.C = is_first ? p.C : p.D; epi.c_dtype = LH_F32; epi.ldc = is_first ? p.scm : p.sdm;
     epi.bias = is_last ? p.bias : nullptr; epi.bias_dtype = p.bias_dtype;
@@ -715,7 +761,10 @@ int gemm_tc_tf32x3_launch(lh_ctx* ctx, const GemmProblem& p) {
     epi.act = is_last ? p.act : LH_ACT_NONE;
     epi.swiglu = 0;
     epi.rope_table = nullptr; epi.rope_cols = 0; epi.rope_dim = 0; epi.rope_seq = 0;
-    rc = wide ? launch_variant<256, true, 4, true, true>(ctx, q, epi) : launch_variant<128, true, 6, true, true>(ctx, q, epi);
+    const int seg_k_blocks = 3 * TF32X3_SEGMENT / (BK / 2);  // a full segment is 768 tf32 columns = 24 k-blocks of 32
+    rc = wide        ? launch_variant<256, true, 4, true, true, 2>(ctx, q, epi, seg_k_blocks)
+         : bn == 128 ? launch_variant<128, true, 6, true, true, 4>(ctx, q, epi, seg_k_blocks)
+                     : launch_variant<64, true, 8, true, true, 4>(ctx, q, epi, seg_k_blocks);
     if (rc) return rc;
   }
   return LH_OK;

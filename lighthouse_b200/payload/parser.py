@@ -547,8 +547,16 @@ class _Parser:
             if txt.startswith("0x"):
                 import struct
 
+                # a hexadecimal float constant is the bit pattern at the type's own width
                 bits = int(txt, 16)
-                op.attrs["value"] = struct.unpack("<f", struct.pack("<I", bits))[0] if t == "f32" else float("nan")
+                if t == "bf16":
+                    op.attrs["value"] = struct.unpack("<f", struct.pack("<I", (bits & 0xFFFF) << 16))[0]
+                elif t == "f16":
+                    op.attrs["value"] = float(struct.unpack("<e", struct.pack("<H", bits & 0xFFFF))[0])
+                elif t == "f64":
+                    op.attrs["value"] = struct.unpack("<d", struct.pack("<Q", bits))[0]
+                else:
+                    op.attrs["value"] = struct.unpack("<f", struct.pack("<I", bits & 0xFFFFFFFF))[0]
             else:
                 op.attrs["value"] = float(txt)
         else:

@@ -7,11 +7,17 @@ from __future__ import annotations
 from .ir import AffineMap, Block, Func, Operation, PayloadModule, ShapedType
 
 
-def _fmt_float(v: float) -> str:
+# bit patterns of NaN, +inf, -inf at each float type's width (MLIR reads a hexadecimal float
+# constant as the bits of its own type)
+_SPECIAL_BITS = {"f32": ("0x7FC00000", "0x7F800000", "0xFF800000"), "bf16": ("0x7FC0", "0x7F80", "0xFF80"),
+                 "f16": ("0x7E00", "0x7C00", "0xFC00"), "f64": ("0x7FF8000000000000", "0x7FF0000000000000", "0xFFF0000000000000")}
+
+
+def _fmt_float(v: float, t: str = "f32") -> str:
     if v != v:
-        return "0x7FC00000"
+        return _SPECIAL_BITS[t][0]
     if v in (float("inf"), float("-inf")):
-        return "0x7F800000" if v > 0 else "0xFF800000"
+        return _SPECIAL_BITS[t][1 if v > 0 else 2]
     s = f"{v:.6e}"
     if float(s) != v:
         s = repr(float(v))
@@ -46,7 +52,7 @@ def _print_op(op: Operation, ind: str, out: list[str]) -> None:
     if n == "arith.constant":
         t = op.results[0].type
         val = op.attrs["value"]
-        txt = _fmt_float(float(val)) if t in ("f16", "bf16", "f32", "f64") else str(int(val))
+        txt = _fmt_float(float(val), str(t)) if t in ("f16", "bf16", "f32", "f64") else str(int(val))
         out.append(f"{ind}{res}arith.constant {txt} : {t}")
     elif n == "tensor.empty":
         out.append(f"{ind}{res}tensor.empty() : {op.results[0].type}")

@@ -92,6 +92,18 @@ def test_oracle_restatement_agrees_with_the_plans_on_other_data(g):
 
 
 # ------------------------------------------------------------------------------------------ GPU
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+def test_index_built_causal_mask_is_recognised_at_every_float_width(dtype):
+    """-inf prints as the bit pattern of the mask's own element type and reads back as -inf,
+    so that the masked attention becomes one causal flash-attention operator."""
+    from lighthouse_b200.payload import as_payload_module
+
+    module = generate_llama_transformer_payload("payload", 1, 128, 256, 2, 1, llama_hidden_dim(256, 64), 1, dtype=dtype, mask="causal", final_norm=False)
+    plan = as_payload_module(str(module)).plans["payload"]
+    attn = [op for op in plan.ops if op.kind == "attention"]
+    assert len(attn) == 1 and attn[0].attrs["causal"]
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("mask", ["operand", "causal"])
 def test_llama_transformer_payload_on_the_gpu_matches_the_reference_ground_truth(ctx, g, mask):

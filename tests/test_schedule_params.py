@@ -44,13 +44,13 @@ def test_selector_database_model_and_apply(tmp_path):
     sel = CudaTileSelector()  # the committed database
     hit = sel.lookup(4096, 4096, 4096)
     assert hit["source"] == "database" and hit["tile_n"] == 256 and hit["layer_kind"] == "matmul"
-    miss = sel.lookup(8192, 768, 4096)  # 64 x 3 tiles of 256 = 2 waves; 64 x 4 tiles of 192 = 2 cheaper waves
+    miss = sel.lookup(8192, 768, 2048)  # 64 x 3 tiles of 256 = 2 waves; 64 x 4 tiles of 192 = 2 cheaper waves
     assert miss["source"] == "model" and miss["tile_n"] == 192
     assert sel.model_choice(16384, 4096, 4096) == 256
 
-    plan = gemm_plan(8192, 768, 4096)
+    plan = gemm_plan(8192, 768, 2048)
     params = sel.select(plan)
-    assert len(params) == 1 and params[0]["shape"] == [8192, 768, 4096]
+    assert len(params) == 1 and params[0]["shape"] == [8192, 768, 2048]
     sel.apply(plan, params)
     assert plan.ops[0].attrs["tile_n"] == 192
     # the hint travels in bits 8-15 of the native flags, the documented flags stay in the low bits
