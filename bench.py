@@ -216,12 +216,13 @@ def decoder_parity(which: str, cfg, w, host_in, dev_out, tp_rank: int, tp: int) 
     rows = torch.from_numpy(P.prefix_rows(cfg.seq, seqs, prefix)).to(dev_out.device)
     got = dev_out[rows].float().cpu().numpy()
     if which == "llama":
-        ref = P.llama_prefix_reference(w, host_in, cfg, seqs, prefix)
+        ref = P.llama_prefix_reference(w, host_in, cfg, seqs, prefix, shards=tp)
     else:
         vl = cfg.vocab // tp
         ref = P.nanogpt_prefix_reference(w, host_in, cfg, seqs, prefix, vocab_slice=slice(tp_rank * vl, (tp_rank + 1) * vl))
     rep = parity_report(got, ref, "bf16", n_layer=cfg.n_layer)
-    rep.update(checked="positions 0..255 of sequences %d and %d of rank 0's result at full depth vs the CPU oracle on those prefixes" % seqs,
+    rep.update(checked="positions 0..255 of sequences %d and %d of rank 0's result at full depth vs the CPU oracle on those prefixes" % seqs
+               + (" (the oracle rounds the %d devices' partial sums of each contracting product as the devices do)" % tp if which == "llama" and tp > 1 else ""),
                max_rel_err=float("%.3e" % rep["max_rel_err"]), elementwise_excess=round(rep["elementwise_excess"], 3))
     return rep
 
@@ -420,9 +421,9 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
 # and attention workloads as they are; the decoder's GEMM launches on a 2-layer stack, summed
 # per layer and multiplied by the layer count, traffic being the same for every layer).
 NCU_TRAFFIC_BYTES = {"gemm_4096": 92.8e6, "attention_full": 250.8e6}
-# The f32 GEMM runs as three tf32 products per f32 product, and the tensor cores run tf32 at
-# half their bf16 rate: its ceiling is a sixth of the measured bf16 peak.
-F32_VIA_TF32X3_FRACTION_OF_BF16 = 1.0 / 6.0
+# The f32 GEMM runs as six bf16 products per f32 product (each operand split into three bf16
+# terms): its ceiling is a sixth of the measured bf16 peak.
+F32_VIA_SIX_BF16_FRACTION_OF_BF16 = 1.0 / 6.0
 
 
 L2_BYTES = 126 << 20
@@ -435,11 +436,13 @@ def rotating_sets(make_set, bytes_per_set: int) -> list:
     return [make_set() for _ in range(n)]
 
 
-def time_rotating(ctx, sess, arg_sets, steps: int, warmup: int):
-    """Seconds per launch, one CUDA-event pair per launch on the context's stream, each launch
-    on the next operand set (inputs larger than L2 in aggregate: every launch finds its
-    operands in HBM, and no flush kernel leaves the cache full of dirty lines for the timed
-    kernel to write back)."""
+def time_rotating(ctx, sess, arg_sets, steps: int, warmup: int, groups: int = 5):
+    """Seconds per launch: ``groups`` CUDA-event pairs on the context's stream, each around
+    ``steps`` launches issued back to back, each launch on the next operand set (inputs larger
+    than L2 in aggregate: every launch finds its operands in HBM, and no flush kernel leaves the
+    cache full of dirty lines for the timed kernel to write back). One array entry per group:
+    its elapsed time / ``steps``, so the gaps between consecutive launches are inside the figure
+    and the cost of recording an event (microseconds, as much as a small kernel) is not."""
     import numpy as np
     import torch
 
@@ -448,16 +451,19 @@ def time_rotating(ctx, sess, arg_sets, steps: int, warmup: int):
     n = len(arg_sets)
     for i in range(warmup):
         sess.run(arg_sets[i % n])
-    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    for i, (e0, e1) in enumerate(pairs):
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(groups)]
+    i = warmup
+    for e0, e1 in pairs:
         e0.record(stream)
-        sess.run(arg_sets[(warmup + i) % n])
+        for _ in range(steps):
+            sess.run(arg_sets[i % n])
+            i += 1
         e1.record(stream)
     ctx.sync()
-    return np.array([e0.elapsed_time(e1) * 1e-3 for e0, e1 in pairs])
+    return np.array([e0.elapsed_time(e1) * 1e-3 / steps for e0, e1 in pairs])
 
 
-L2_NOTE = "operand sets rotate (3 x L2 in aggregate): every timed launch reads its operands from HBM"
+L2_NOTE = "operand sets rotate (3 x L2 in aggregate): every timed launch reads its operands from HBM; launches back to back, one event pair per group of launches"
 
 
 def kernel_gemm(ctx, peaks, source, K=4096, steps=20, warmup=5) -> dict:
@@ -491,8 +497,9 @@ def kernel_gemm(ctx, peaks, source, K=4096, steps=20, warmup=5) -> dict:
 
 def kernel_gemm_f32(ctx, peaks, source, steps=20, warmup=5) -> dict:
     """f32 GEMM accumulating into C, M = N = K = 1024, A, B ~ U(-1, 1) (config 1): the lh-run
-    matmul. Runs as 3 x TF32 on the tensor cores (two operand-split launches + one tcgen05
-    GEMM over 3K); the flop count is the f32 problem's 2MNK."""
+    matmul. Runs as six bf16 products on the tensor cores (one operand-split launch + one
+    tcgen05 GEMM over 6K with four accumulators per tile); the flop count is the f32 problem's
+    2MNK."""
     import torch
 
     from lighthouse_b200.plan import ArgSpec, Plan
@@ -509,11 +516,11 @@ def kernel_gemm_f32(ctx, peaks, source, steps=20, warmup=5) -> dict:
     sess.close()
     mean_s = float(times.mean())
     achieved = 2.0 * M * N * K / mean_s / 1e12
-    peak = peaks["bf16_tflops"] * F32_VIA_TF32X3_FRACTION_OF_BF16
+    peak = peaks["bf16_tflops"] * F32_VIA_SIX_BF16_FRACTION_OF_BF16
     return {"ms": round(mean_s * 1e3, 5), "best_ms": round(float(times.min()) * 1e3, 5), "tflops": round(achieved, 2), "shape": [M, N, K],
-            "path": "3xTF32 tcgen05; f32 result within 1e-5 of the loop nest",
-            "roofline": {"bound": "tensor", "kernel": "gemm_bf16_tc_kernel<tf32>", "achieved": round(achieved, 2), "peak": round(peak, 1), "unit": "TFLOP/s",
-                         "frac": round(achieved / peak, 4), "peak_source": f"{source} cuBLAS bf16 burst / 6: tf32 at half the bf16 rate, three tf32 products per f32 product", "traffic": None},
+            "path": "six bf16 products (operands split in three bf16 terms) on tcgen05, two launches; f32 result within 1e-5 of the loop nest",
+            "roofline": {"bound": "tensor", "kernel": "split_bf16x3_kernel + gemm_bf16_tc_kernel<4 accumulators>", "achieved": round(achieved, 2), "peak": round(peak, 1), "unit": "TFLOP/s",
+                         "frac": round(achieved / peak, 4), "peak_source": f"{source} cuBLAS bf16 burst / 6: six bf16 products per f32 product", "traffic": None},
             "reference_published_cpu_gflops": 137.91}
 
 

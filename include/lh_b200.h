@@ -157,7 +157,8 @@ int lh_b200_host_free(void* ptr);
  * lighthouse/utils/mlir.py:146-173). Rank-3 operands are a batched product
  * (linalg.batch_matmul). bf16 operands whose rows are 16-byte aligned with unit
  * inner stride run on the tcgen05 tensor-core kernel; f32 operands run on the
- * 3xTF32 tensor-core kernel or the FFMA kernel; everything else runs on the
+ * tensor cores as six bf16 products (each operand split into three bf16 terms,
+ * f32 accumulation) or on the FFMA kernel; everything else runs on the
  * generic CUDA-core kernel.
  * `c` and `residual` may alias `d`.
  */

@@ -358,7 +358,7 @@ extern "C" int lh_b200_gemm(lh_ctx_t* ctx, const lh_memref_t* d, const lh_memref
     return lh_b200_memset(ctx, g.D, 0, static_cast<size_t>(numel(d)) * dtype_size(d->dtype));
   }
   if (gemm_tc_bf16_supported(ctx, g)) return gemm_tc_bf16_launch(ctx, g);
-  if (gemm_tc_tf32x3_supported(ctx, g)) return gemm_tc_tf32x3_launch(ctx, g);
+  if (gemm_tc_split_f32_supported(ctx, g)) return gemm_tc_split_f32_launch(ctx, g);
   return gemm_simt_launch(ctx, g);
 }
 
@@ -662,7 +662,7 @@ size_t op_scratch_bytes(const lh_op_t& op) {
     const lh_view_t& a = op.operands[1];
     const lh_view_t& b = op.operands[2];
     if (a.slot < 0 || b.slot < 0 || a.rank != 2 || a.dtype != LH_F32 || b.dtype != LH_F32) return 0;
-    return gemm_tc_tf32x3_scratch_bytes(static_cast<int>(a.shape[0]), static_cast<int>(b.shape[1]), static_cast<int>(a.shape[1]));
+    return gemm_tc_split_f32_scratch_bytes(static_cast<int>(a.shape[0]), static_cast<int>(b.shape[1]), static_cast<int>(a.shape[1]));
   }
   return 0;
 }

@@ -148,9 +148,9 @@ struct EpiParams {
 
 int gemm_tc_bf16_supported(const lh_ctx* ctx, const GemmProblem& p);
 int gemm_tc_bf16_launch(lh_ctx* ctx, const GemmProblem& p);
-int gemm_tc_tf32x3_supported(const lh_ctx* ctx, const GemmProblem& p);
-int gemm_tc_tf32x3_launch(lh_ctx* ctx, const GemmProblem& p);
-size_t gemm_tc_tf32x3_scratch_bytes(int M, int N, int K);  // 0 where the 3xTF32 path does not apply
+int gemm_tc_split_f32_supported(const lh_ctx* ctx, const GemmProblem& p);
+int gemm_tc_split_f32_launch(lh_ctx* ctx, const GemmProblem& p);
+size_t gemm_tc_split_f32_scratch_bytes(int M, int N, int K);  // 0 where the split-f32 tensor-core path does not apply
 int gemm_simt_launch(lh_ctx* ctx, const GemmProblem& p);
 
 // -------------------------------------------------------- attention problem

@@ -161,20 +161,17 @@ __device__ __forceinline__ void load_row_segment(uint4 (&seg)[8], const void* ba
   }
 }
 
-// TF32: the operands are f32 arrays read as tf32 (kind::tf32, K = 8 per instruction, 32
-// elements per 128-byte swizzle row); everything else - ring, tensor memory, epilogue - is the
-// bf16 kernel's.
-// SEGS > 1 (the 3 x TF32 path): the k range is cut into up to SEGS segments, each summed
+// SEGS > 1 (the split-f32 path below): the k range is cut into up to SEGS segments, each summed
 // in its own accumulator (SEGS * BN columns of tensor memory, no double buffering across tiles)
 // and the segments' sums are added with correctly rounded f32 adds in the epilogue: the tensor
 // core adds into an accumulator with truncation, which biases long sums.
-template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, bool TF32 = false, int SEGS = 1>
+template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, int SEGS = 1>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmD, const GemmTcParams p) {
   using L = SmemLayout<BN, STAGES>;
   constexpr int TMEM_COLS = SEGS > 1 ? tmem_cols_for((SEGS * BN + 1) / 2) : tmem_cols_for(BN);
-  static_assert(SEGS == 1 || (TF32 && SEGS * BN <= 512), "segmented accumulation is the tf32 path's");
+  static_assert(SEGS == 1 || (B_KMAJOR && OUT_F32 && SEGS * BN <= 512), "segmented accumulation is the split-f32 path's");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 
@@ -188,8 +185,6 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
-  constexpr int BKE = TF32 ? BK / 2 : BK;  // elements per k-block (always 128 bytes)
-  static_assert(!TF32 || (B_KMAJOR && OUT_F32), "the tf32 variant takes k-major B and writes f32");
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -232,9 +227,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           uint8_t* sA = smem + stage * L::STAGE_BYTES;
           uint8_t* sB = sA + A_TILE_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
-          tma_load_2d(sA, &tmA, &full_bar[stage], kb * BKE, m_blk * BM);
+          tma_load_2d(sA, &tmA, &full_bar[stage], kb * BK, m_blk * BM);
           if (B_KMAJOR) {
-            tma_load_2d(sB, &tmB, &full_bar[stage], kb * BKE, n_blk * BN);
+            tma_load_2d(sB, &tmB, &full_bar[stage], kb * BK, n_blk * BN);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
@@ -250,7 +245,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(TF32 ? UMMA_TF32 : UMMA_BF16, BM, BN, false, !B_KMAJOR);
+      constexpr uint32_t idesc = make_idesc(UMMA_BF16, BM, BN, false, !B_KMAJOR);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -276,8 +271,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint64_t adesc = make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
             const uint64_t bdesc = B_KMAJOR ? make_smem_desc_sw128(b_addr + k * 32, 16, 1024)
                                             : make_smem_desc_sw128(b_addr + k * 2048, 64 * BK * 2, 1024);
-            if (TF32) umma_tf32_ss(d_tmem, adesc, bdesc, idesc, (kb_in_seg | k) != 0 ? 1u : 0u);
-            else umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb_in_seg | k) != 0 ? 1u : 0u);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb_in_seg | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == STAGES) {
@@ -464,25 +458,24 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
-template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, bool TF32 = false, int SEGS = 1>
+template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, int SEGS = 1>
 int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int seg_k_blocks = 0) {
   using L = SmemLayout<BN, STAGES>;
   CUtensorMap tmA, tmB, tmD;
   const int n_out = epi.swiglu ? pr.N / 2 : pr.N;
-  constexpr uint32_t BKE = TF32 ? BK / 2 : BK;
-  constexpr uint64_t ab_size = TF32 ? 4 : 2;
-  constexpr int ab_dtype = TF32 ? LH_F32 : LH_BF16;
+  constexpr uint64_t ab_size = 2;
+  constexpr int ab_dtype = LH_BF16;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(pr.K), static_cast<uint64_t>(pr.M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(pr.sam) * ab_size};
-    const uint32_t box[2] = {BKE, BM};
+    const uint32_t box[2] = {BK, BM};
     int rc = encode_tensor_map(ctx, &tmA, ab_dtype, 2, const_cast<void*>(pr.A), dims, strides, box, 1);
     if (rc) return rc;
   }
   if (B_KMAJOR) {  // B(k,n) with unit k stride: a row-major (N,K) array
     const uint64_t dims[2] = {static_cast<uint64_t>(pr.K), static_cast<uint64_t>(pr.N)};
     const uint64_t strides[1] = {static_cast<uint64_t>(pr.sbn) * ab_size};
-    const uint32_t box[2] = {BKE, BN};
+    const uint32_t box[2] = {BK, BN};
     int rc = encode_tensor_map(ctx, &tmB, ab_dtype, 2, const_cast<void*>(pr.B), dims, strides, box, 1);
     if (rc) return rc;
   } else {  // B(k,n) with unit n stride: a row-major (K,N) array
@@ -507,7 +500,7 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int
   p.n_out = n_out;
   p.num_m_blocks = (pr.M + BM - 1) / BM;
   p.num_n_blocks = (pr.N + BN - 1) / BN;
-  p.num_k_blocks = (pr.K + static_cast<int>(BKE) - 1) / static_cast<int>(BKE);
+  p.num_k_blocks = (pr.K + BK - 1) / BK;
   // Widest group whose A panel (group_m x 128 rows x K) stays within a quarter of L2: 64
   // row-blocks up to K = 2048, 32 up to 4096, 16 beyond (measured at 16 with K = 4096,
   // N = 28672: B read 8 times, 2.0 GB of DRAM reads for 0.37 GB of operands).
@@ -519,7 +512,7 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int
   p.epi = epi;
   p.seg_k_blocks = seg_k_blocks > 0 ? seg_k_blocks : p.num_k_blocks;
   p.dev_status = ctx->dev_status;
-  auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES, OUT_F32, TF32, SEGS>;
+  auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES, OUT_F32, SEGS>;
   LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
   // A persistent grid that fills the GPU would make side-stream kernels (collectives) wait for
@@ -620,82 +613,108 @@ int gemm_tc_bf16_launch(lh_ctx* ctx, const GemmProblem& p) {
   return out_f32 ? launch_bn<false, true>(ctx, p, epi, bn) : launch_bn<false, false>(ctx, p, epi, bn);
 }
 
-// ------------------------------------------------------------------ f32 GEMM as 3 x TF32
-// tf32 keeps 10 mantissa bits, so one tf32 product is not an f32 product. Each operand is
-// split into a tf32-exact head and the (f32-exact) remainder, hi = x with the low 13 mantissa
-// bits cleared, lo = x - hi, and the product is summed as hi*hi + lo*hi + hi*lo with f32
-// accumulation in tensor memory: the dropped lo*lo term and the truncation of lo are ~2^-21
-// relative. The three partial products are one tf32 GEMM over a concatenated k dimension:
-//   A' (M, 3K) = [A_hi | A_lo | A_hi],   B' (N, 3K) = [B_hi | B_hi | B_lo]  (both k-major)
-// written by split_tf32_kernel into context scratch (which also transposes B as needed).
+// ------------------------------------------------------------- f32 GEMM as six bf16 products
+// Each f32 operand is split into three bf16 terms, x = h + m + l exactly up to 2^-24 |x|:
+// h = bf16(x), m = bf16(x - h), l = bf16(x - h - m) (both differences are exact in f32). The
+// f32 product is summed from the six bf16 products whose weight is at least 2^-16,
+//   h*h + h*m + m*h + m*m + h*l + l*h     (dropped: m*l, l*m, l*l, about 2^-24 relative),
+// with f32 accumulation in tensor memory. The six products are one bf16 GEMM over a
+// concatenated k dimension,
+//   A' (M, 6K) = [A_h | A_h | A_m | A_m | A_h | A_l],   B' (N, 6K) = [B_h | B_m | B_h | B_m | B_l | B_h]
+// (both k-major), written by split_bf16x3_kernel into context scratch (which also transposes
+// B as needed). Against three tf32 products of a (head, remainder) split the operand bytes are
+// the same and the instruction count too, but a bf16 instruction covers twice the k.
 // The tensor core adds into its f32 accumulator with truncation, a bias towards zero of about
-// 3e-8 of the sum per instruction (measured: 1.2e-5 over the 375 instructions of K = 1000). So
-// k is cut into segments of TF32X3_SEGMENT: each segment is one launch whose epilogue adds
-// the running result as C with a correctly rounded f32 add, and the concatenation above is
-// per segment.
+// 3e-8 of the sum per instruction. So k is cut into segments of SPLIT_SEGMENT original columns
+// (96 instructions), each summed in its own accumulator, and the segments' sums are added with
+// correctly rounded f32 adds in the epilogue; the concatenation above is per segment. A k range
+// beyond what one launch's accumulators hold takes further launches whose epilogue adds the
+// running result as C.
 namespace {
 
 struct SplitOperand {
   const float* src;
   int64_t s_row, s_k;
   int rows;
-  float* dst;
-  int lo_slot;  // which of a segment's three slots takes the remainder (the other two take the head)
+  __nv_bfloat16* dst;
+  uint32_t slots;  // 2 bits per slot of a segment: which term (0 h, 1 m, 2 l) it takes
 };
 
-// Both operands in one launch: blockIdx.z selects A or B.
-__global__ void __launch_bounds__(256) split_tf32_kernel(const SplitOperand oa, const SplitOperand ob, int K, int64_t ld, int seg) {
-  // 32 rows x 32 k per block through shared memory, so that both the read (along whichever of
-  // row / k is contiguous in src) and the write (along k) are coalesced.
-  __shared__ float tile[32][33];
+constexpr int SPLIT_SEGMENT = 256;                    // original k per accumulator: 96 bf16 instructions
+constexpr int64_t SPLIT_MIN_WORK = 1ll << 21;         // below this the CUDA-core kernel's single launch wins
+constexpr size_t SPLIT_MAX_SCRATCH = 3ull << 30;      // split copies larger than this stay on the CUDA cores
+constexpr uint32_t SLOTS_A = 0u | (0u << 2) | (1u << 4) | (1u << 6) | (0u << 8) | (2u << 10);
+constexpr uint32_t SLOTS_B = 0u | (1u << 2) | (0u << 4) | (1u << 6) | (2u << 8) | (0u << 10);
+
+// Both operands in one launch: blockIdx.z selects A or B. A block handles 32 rows x 64 k
+// through shared memory, so that the read (along whichever of row / k is contiguous in src) is
+// coalesced; each thread then splits 8 consecutive k of one row and writes six 16-byte vectors.
+__global__ void __launch_bounds__(256) split_bf16x3_kernel(const SplitOperand oa, const SplitOperand ob, int K, int64_t ld) {
+  __shared__ float tile[32][65];
   const SplitOperand& o = blockIdx.z == 0 ? oa : ob;
-  const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+  const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 64;
   if (r0 >= o.rows) return;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
-  const bool k_contig = (o.s_k == 1);
-  for (int i = ty; i < 32; i += 8) {
-    const int r = k_contig ? r0 + i : r0 + tx;
-    const int k = k_contig ? k0 + tx : k0 + i;
-    const float v = (r < o.rows && k < K) ? o.src[r * o.s_row + k * o.s_k] : 0.f;
-    if (k_contig) tile[i][tx] = v;
-    else tile[tx][i] = v;
+  if (o.s_k == 1) {
+    // k contiguous: 64 consecutive k of a row per pair of warps
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;  // 64 x 4
+    for (int i = ty; i < 32; i += 4) {
+      const int r = r0 + i, k = k0 + tx;
+      tile[i][tx] = (r < o.rows && k < K) ? o.src[r * o.s_row + k] : 0.f;
+    }
+  } else {
+    // rows contiguous: 32 consecutive rows of one k per warp
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    for (int i = ty; i < 64; i += 8) {
+      const int r = r0 + tx, k = k0 + i;
+      tile[tx][i] = (r < o.rows && k < K) ? o.src[r * o.s_row + k * o.s_k] : 0.f;
+    }
   }
   __syncthreads();
-  for (int i = ty; i < 32; i += 8) {
-    const int r = r0 + i, k = k0 + tx;
-    if (r < o.rows && k < K) {
-      const float x = tile[i][tx];
-      const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
-      const float lo = x - hi;
-      // k belongs to segment k / seg, which owns columns [3 * first, 3 * (first + len)) as
-      // three slots of len; the remainder sits in slot lo_slot, the head in the other two
-      const int first = (k / seg) * seg;
-      const int len = min(seg, K - first);
-      float* out = o.dst + r * ld + 3 * static_cast<int64_t>(first) + (k - first);
-      out[0] = o.lo_slot == 0 ? lo : hi;
-      out[len] = o.lo_slot == 1 ? lo : hi;
-      out[2 * len] = o.lo_slot == 2 ? lo : hi;
-    }
+  const int i = threadIdx.x >> 3, g = threadIdx.x & 7;  // row in the tile, group of 8 k
+  const int r = r0 + i, k = k0 + g * 8;
+  if (r >= o.rows || k >= K) return;
+  __nv_bfloat16 term[3][8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float x = tile[i][g * 8 + e];
+    const __nv_bfloat16 h = __float2bfloat16_rn(x);
+    const float x1 = x - __bfloat162float(h);
+    const __nv_bfloat16 m = __float2bfloat16_rn(x1);
+    const float x2 = x1 - __bfloat162float(m);
+    term[0][e] = h;
+    term[1][e] = m;
+    term[2][e] = __float2bfloat16_rn(x2);
+  }
+  // k belongs to segment k / SPLIT_SEGMENT, which owns columns [6 * first, 6 * (first + len))
+  // as six slots of len; a group of 8 never straddles a segment (segments are multiples of 8)
+  const int first = (k / SPLIT_SEGMENT) * SPLIT_SEGMENT;
+  const int len = min(SPLIT_SEGMENT, K - first);
+  __nv_bfloat16* out = o.dst + r * ld + 6 * static_cast<int64_t>(first) + (k - first);
+  if ((len & 7) == 0) {
+#pragma unroll
+    for (int sl = 0; sl < 6; ++sl)
+      *reinterpret_cast<uint4*>(out + sl * len) = *reinterpret_cast<const uint4*>(term[(o.slots >> (2 * sl)) & 3u]);
+  } else {
+    // a ragged last segment: its slots do not start on 16-byte boundaries
+    const int n = min(8, K - k);
+    for (int sl = 0; sl < 6; ++sl)
+      for (int e = 0; e < n; ++e) out[sl * len + e] = term[(o.slots >> (2 * sl)) & 3u][e];
   }
 }
 
-constexpr int TF32X3_SEGMENT = 256;                   // original k per launch: 96 tf32 instructions per accumulator
-constexpr int64_t TF32X3_MIN_WORK = 1ll << 21;        // below this the CUDA-core kernel's single launch wins
-constexpr size_t TF32X3_MAX_SCRATCH = 3ull << 30;     // split copies larger than this stay on the CUDA cores
-
-inline int64_t tf32x3_ld(int K) { return (3ll * K + 3) & ~3ll; }  // rows 16-byte aligned
+inline int64_t split_ld(int K) { return (6ll * K + 7) & ~7ll; }  // rows 16-byte aligned
 
 }  // namespace
 
-int gemm_tc_tf32x3_supported(const lh_ctx* ctx, const GemmProblem& p) {
+int gemm_tc_split_f32_supported(const lh_ctx* ctx, const GemmProblem& p) {
   if (ctx->cc_major != 10) return 0;
   if (p.flags & (LH_GEMM_FORCE_SIMT | LH_GEMM_SWIGLU)) return 0;
   if (p.batch != 1) return 0;
   if (p.a_dtype != LH_F32 || p.b_dtype != LH_F32 || p.d_dtype != LH_F32) return 0;
   if (p.M < 1 || p.K < 1 || p.N < 8 || p.N % 8) return 0;
-  if (static_cast<int64_t>(p.M) * p.N * p.K < TF32X3_MIN_WORK) return 0;
-  const size_t scratch = static_cast<size_t>(tf32x3_ld(p.K)) * 4 * (static_cast<size_t>(p.M) + p.N);
-  if (scratch > TF32X3_MAX_SCRATCH) return 0;
+  if (static_cast<int64_t>(p.M) * p.N * p.K < SPLIT_MIN_WORK) return 0;
+  const size_t scratch = static_cast<size_t>(split_ld(p.K)) * 2 * (static_cast<size_t>(p.M) + p.N);
+  if (scratch > SPLIT_MAX_SCRATCH) return 0;
   auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
   if (p.sdn != 1 || (p.sdm % 4) != 0 || p.sdm < p.N || !aligned16(p.D)) return 0;
   if (p.C && (p.c_dtype != LH_F32 || p.scn != 1 || (p.scm % 4) != 0 || !aligned16(p.C))) return 0;
@@ -704,33 +723,33 @@ int gemm_tc_tf32x3_supported(const lh_ctx* ctx, const GemmProblem& p) {
   return 1;
 }
 
-size_t gemm_tc_tf32x3_scratch_bytes(int M, int N, int K) {
-  if (M < 1 || K < 1 || N < 8 || N % 8 || static_cast<int64_t>(M) * N * K < TF32X3_MIN_WORK) return 0;
-  const size_t a_bytes = static_cast<size_t>(M) * tf32x3_ld(K) * 4, b_bytes = static_cast<size_t>(N) * tf32x3_ld(K) * 4;
+size_t gemm_tc_split_f32_scratch_bytes(int M, int N, int K) {
+  if (M < 1 || K < 1 || N < 8 || N % 8 || static_cast<int64_t>(M) * N * K < SPLIT_MIN_WORK) return 0;
+  const size_t a_bytes = static_cast<size_t>(M) * split_ld(K) * 2, b_bytes = static_cast<size_t>(N) * split_ld(K) * 2;
   const size_t total = ((a_bytes + 255) & ~static_cast<size_t>(255)) + b_bytes;
-  return total > TF32X3_MAX_SCRATCH ? 0 : total;
+  return total > SPLIT_MAX_SCRATCH ? 0 : total;
 }
 
-int gemm_tc_tf32x3_launch(lh_ctx* ctx, const GemmProblem& p) {
-  const int64_t ld = tf32x3_ld(p.K);
-  const size_t a_bytes = static_cast<size_t>(p.M) * ld * 4, b_bytes = static_cast<size_t>(p.N) * ld * 4;
+int gemm_tc_split_f32_launch(lh_ctx* ctx, const GemmProblem& p) {
+  const int64_t ld = split_ld(p.K);
+  const size_t a_bytes = static_cast<size_t>(p.M) * ld * 2, b_bytes = static_cast<size_t>(p.N) * ld * 2;
   const size_t a_pad = (a_bytes + 255) & ~static_cast<size_t>(255);
   int rc = ensure_scratch(ctx, a_pad + b_bytes);
   if (rc) return rc;
-  float* a3 = static_cast<float*>(ctx->scratch);
-  float* b3 = reinterpret_cast<float*>(static_cast<char*>(ctx->scratch) + a_pad);
+  __nv_bfloat16* a6 = static_cast<__nv_bfloat16*>(ctx->scratch);
+  __nv_bfloat16* b6 = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ctx->scratch) + a_pad);
   {
-    const SplitOperand oa{static_cast<const float*>(p.A), p.sam, p.sak, p.M, a3, 1};
-    const SplitOperand ob{static_cast<const float*>(p.B), p.sbn, p.sbk, p.N, b3, 2};
+    const SplitOperand oa{static_cast<const float*>(p.A), p.sam, p.sak, p.M, a6, SLOTS_A};
+    const SplitOperand ob{static_cast<const float*>(p.B), p.sbn, p.sbk, p.N, b6, SLOTS_B};
     const int max_rows = p.M > p.N ? p.M : p.N;
-    const dim3 grid((p.K + 31) / 32, (max_rows + 31) / 32, 2);
-    split_tf32_kernel<<<grid, 256, 0, ctx->stream>>>(oa, ob, p.K, ld, TF32X3_SEGMENT);
-    LH_CHECK_LAUNCH(ctx, "split_tf32_kernel");
+    const dim3 grid((p.K + 63) / 64, (max_rows + 31) / 32, 2);
+    split_bf16x3_kernel<<<grid, 256, 0, ctx->stream>>>(oa, ob, p.K, ld);
+    LH_CHECK_LAUNCH(ctx, "split_bf16x3_kernel");
   }
   const int sms = ctx->sm_count - ctx->reserved_sms > 0 ? ctx->sm_count - ctx->reserved_sms : 1;
   const int64_t num_m = (p.M + BM - 1) / BM;
   const int64_t tiles256 = num_m * ((p.N + 255) / 256), tiles128 = num_m * ((p.N + 127) / 128);
-  const int nseg = (p.K + TF32X3_SEGMENT - 1) / TF32X3_SEGMENT;
+  const int nseg = (p.K + SPLIT_SEGMENT - 1) / SPLIT_SEGMENT;
   // Small and medium products: 64- or 128-wide tiles (whichever still gives every SM a tile)
   // with four segment accumulators each, so a whole k range of 1024 is ONE launch (launch
   // latency is what such products cost). Large ones: the wider tile's efficiency matters more
@@ -744,13 +763,14 @@ int gemm_tc_tf32x3_launch(lh_ctx* ctx, const GemmProblem& p) {
   const int per_launch = wide ? 2 : 4;
   for (int s0 = 0; s0 < nseg; s0 += per_launch) {
     const int s1 = s0 + per_launch < nseg ? s0 + per_launch : nseg;
-    const int first = s0 * TF32X3_SEGMENT;
-    const int last_k = s1 * TF32X3_SEGMENT < p.K ? s1 * TF32X3_SEGMENT : p.K;
+    const int first = s0 * SPLIT_SEGMENT;
+    const int last_k = s1 * SPLIT_SEGMENT < p.K ? s1 * SPLIT_SEGMENT : p.K;
     const bool is_first = s0 == 0, is_last = s1 == nseg;
     GemmProblem q = p;
-    q.K = 3 * (last_k - first);
-    q.A = a3 + 3 * static_cast<int64_t>(first); q.sam = ld; q.sak = 1;
-    q.B = b3 + 3 * static_cast<int64_t>(first); q.sbn = ld; q.sbk = 1;
+    q.a_dtype = LH_BF16; q.b_dtype = LH_BF16;
+    q.K = 6 * (last_k - first);
+    q.A = a6 + 6 * static_cast<int64_t>(first); q.sam = ld; q.sak = 1;
+    q.B = b6 + 6 * static_cast<int64_t>(first); q.sbn = ld; q.sbk = 1;
     EpiParams epi;
     epi.D = p.D; epi.d_dtype = p.d_dtype; epi.ldd = p.sdm;
     // the caller's C enters with the first launch, the running sum (D) with the later ones;
@@ -761,10 +781,10 @@ int gemm_tc_tf32x3_launch(lh_ctx* ctx, const GemmProblem& p) {
     epi.act = is_last ? p.act : LH_ACT_NONE;
     epi.swiglu = 0;
     epi.rope_table = nullptr; epi.rope_cols = 0; epi.rope_dim = 0; epi.rope_seq = 0;
-    const int seg_k_blocks = 3 * TF32X3_SEGMENT / (BK / 2);  // a full segment is 768 tf32 columns = 24 k-blocks of 32
-    rc = wide        ? launch_variant<256, true, 4, true, true, 2>(ctx, q, epi, seg_k_blocks)
-         : bn == 128 ? launch_variant<128, true, 6, true, true, 4>(ctx, q, epi, seg_k_blocks)
-                     : launch_variant<64, true, 8, true, true, 4>(ctx, q, epi, seg_k_blocks);
+    const int seg_k_blocks = 6 * SPLIT_SEGMENT / BK;  // a full segment is 1536 bf16 columns = 24 k-blocks of 64
+    rc = wide        ? launch_variant<256, true, 4, true, 2>(ctx, q, epi, seg_k_blocks)
+         : bn == 128 ? launch_variant<128, true, 6, true, 4>(ctx, q, epi, seg_k_blocks)
+                     : launch_variant<64, true, 8, true, 4>(ctx, q, epi, seg_k_blocks);
     if (rc) return rc;
   }
   return LH_OK;

@@ -35,12 +35,14 @@ class _LazyLayers:
             yield tree_to_np(lw)
 
 
-def llama_prefix_reference(weights: dict, x, cfg, sequences=(0, 1), prefix: int = 256) -> np.ndarray:
+def llama_prefix_reference(weights: dict, x, cfg, sequences=(0, 1), prefix: int = 256, shards: int = 1) -> np.ndarray:
     """(len(sequences) * prefix, dim) oracle output for the first ``prefix`` positions of the
     chosen sequences of ``x`` ((batch * seq, dim), torch bf16 or numpy); ``weights`` in the
-    reference's (out, in) layout as ``workloads.synthetic.llama_weights`` makes them."""
+    reference's (out, in) layout as ``workloads.synthetic.llama_weights`` makes them.
+    ``shards``: the tensor-parallel degree of the run under test (the contracting products'
+    partial sums are then rounded per device, see ``reference_ops.sharded_contraction``)."""
     xs = to_np(x).reshape(cfg.batch, cfg.seq, cfg.dim)[list(sequences), :prefix]
-    out = R.llama_forward(xs, _LazyLayers(weights["layers"]), to_np(weights["norm"]), cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True, fused_residual=True)
+    out = R.llama_forward(xs, _LazyLayers(weights["layers"]), to_np(weights["norm"]), cfg.n_heads, cfg.n_kv_heads, cfg.theta, cfg.eps, "bf16", fused_swiglu=True, fused_residual=True, shards=shards)
     return out.reshape(len(sequences) * prefix, cfg.dim)
 
 

@@ -44,7 +44,7 @@ def test_gemm_f32_matches_loop_nest(ctx, shape):
 
 @pytest.mark.parametrize("shape", [(300, 264, 77), (129, 512, 1000), (2048, 128, 9)])
 def test_gemm_f32_tensor_core_split_path(ctx, shape):
-    """Shapes large enough for the 3 x TF32 tensor-core path (N a multiple of 8), ragged in M
+    """Shapes large enough for the split-f32 (six bf16 products) tensor-core path (N a multiple of 8), ragged in M
     and K, accumulating into C, with bias, activation and residual, and with transposed
     operand views: within the f32 tolerance of the loop nest."""
     m, n, k = shape

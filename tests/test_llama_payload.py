@@ -116,7 +116,7 @@ def test_llama_transformer_payload_on_the_gpu_matches_the_reference_ground_truth
     runner.execute("payload", transformer_args(g, nl, mask), Runner.get_gpu_argument_access_callback(out))
     runner.close()
     assert np.allclose(out, g["out"], rtol=0.01, atol=0.01)  # the reference's own criterion
-    assert_parity(out, g["out"], "f32", tol=1e-4)  # f32 on the CUDA cores / 3xTF32: accumulation order differs from torch's
+    assert_parity(out, g["out"], "f32", tol=1e-4)  # f32 on the CUDA cores / six bf16 products: accumulation order differs from torch's
 
 
 @pytest.mark.gpu

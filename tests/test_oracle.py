@@ -236,3 +236,20 @@ def test_llama_linalg_restatement_matches_the_reference_tests_ground_truth():
     assert_close(R.llama_linalg_attention(g["x"], l0["wq"], l0["wk"], l0["wv"], l0["wo"], g["freqs_real"], g["mask"], nh, nkv), g["attn_out"], "f32", "get_attention")
     assert_close(R.llama_linalg_block(g["x"], l0, g["freqs_real"], g["mask"], nh, nkv), g["block0_out"], "f32", "get_transformer_block")
     assert_close(R.llama_linalg_transformer(g["x"], layers, g["freqs_real"], g["mask"], nh, nkv), g["out"], "f32", "get_transformer")
+
+
+def test_sharded_contraction_rounds_per_device_and_agrees_with_the_plain_product():
+    """One shard is the rounded product; several shards round each partial sum and the total,
+    which moves a bf16 result by a few units in the last place and an f32 one not at all
+    beyond summation order."""
+    rng = np.random.default_rng(5)
+    a = R.round_bf16(rng.standard_normal((24, 64)).astype(np.float32))
+    w = R.round_bf16(rng.standard_normal((16, 64)).astype(np.float32) * 0.1)
+    plain = R.round_bf16(a @ w.T)
+    assert np.array_equal(R.sharded_contraction(a, w, 1, "bf16"), plain)
+    two = R.sharded_contraction(a, w, 2, "bf16")
+    assert not np.array_equal(two, plain)
+    assert np.max(np.abs(two - plain)) <= 3 * 2.0**-8 * np.max(np.abs(plain))
+    np.testing.assert_allclose(R.sharded_contraction(a, w, 4, "f32"), a @ w.T, rtol=1e-5, atol=1e-6)
+    with pytest.raises(ValueError):
+        R.sharded_contraction(a, w, 3, "bf16")
