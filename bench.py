@@ -220,7 +220,9 @@ def decoder_parity(which: str, cfg, w, host_in, dev_out, tp_rank: int, tp: int) 
     else:
         vl = cfg.vocab // tp
         ref = P.nanogpt_prefix_reference(w, host_in, cfg, seqs, prefix, vocab_slice=slice(tp_rank * vl, (tp_rank + 1) * vl))
-    rep = parity_report(got, ref, "bf16", n_layer=cfg.n_layer)
+    from oracle.check import LAYER_ROUNDINGS, SHARDED_LAYER_ROUNDINGS
+
+    rep = parity_report(got, ref, "bf16", n_layer=cfg.n_layer, roundings_per_layer=SHARDED_LAYER_ROUNDINGS if which == "llama" and tp > 1 else LAYER_ROUNDINGS)
     rep.update(checked="positions 0..255 of sequences %d and %d of rank 0's result at full depth vs the CPU oracle on those prefixes" % seqs
                + (" (the oracle rounds the %d devices' partial sums of each contracting product as the devices do)" % tp if which == "llama" and tp > 1 else ""),
                max_rel_err=float("%.3e" % rep["max_rel_err"]), elementwise_excess=round(rep["elementwise_excess"], 3))

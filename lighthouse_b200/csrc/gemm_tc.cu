@@ -40,6 +40,8 @@ struct GemmTcParams {
   int num_m_blocks, num_n_blocks, num_k_blocks;
   int group_m;  // row-blocks per rasterisation group
   int seg_k_blocks;  // SEGS > 1: k-blocks per accumulator
+  int num_items;        // work items: full tiles, then the last partial wave's tiles as two half-width items each
+  int first_half_item;  // items from here on are half tiles (== num_items when the tail is not split)
   EpiParams epi;
   int* dev_status;
 };
@@ -51,6 +53,7 @@ __host__ __device__ constexpr int tmem_cols_for(int bn) {
 template <int BN, int STAGES>
 struct SmemLayout {
   static constexpr int B_TILE_BYTES = BN * BK * 2;
+  static constexpr int B_BOX_ROWS = BN == 256 ? 128 : BN;  // k-major B: rows per TMA box (a half tile is one box of the widest tile)
   static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
   static constexpr int STAGING_OFFSET = STAGES * STAGE_BYTES;  // multiple of 1024
   static constexpr int BAR_OFFSET = STAGING_OFFSET + STAGING_BYTES;
@@ -72,6 +75,27 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int 
   const int in_group = tile - group * group_size;
   m_blk = first_m + in_group % rows;
   n_blk = in_group / rows;
+}
+
+// Work item -> (tile, which half, is it a half). When the tiles do not fill the grid's last
+// wave and twice the remainder still fits the grid, the remaining tiles are walked as two
+// half-width items each: the last wave then takes about 0.6 of a tile's time instead of a
+// whole one while most of the SMs idle.
+struct WorkItem {
+  int tile, half;
+  bool is_half;
+};
+__device__ __forceinline__ WorkItem work_item(int it, int first_half_item) {
+  if (it < first_half_item) return {it, 0, false};
+  const int h = it - first_half_item;
+  return {first_half_item + (h >> 1), h & 1, true};
+}
+
+// Every lane observes the phase itself (its later accesses are ordered after it); the warp
+// agrees on the verdict so that a wait that ran out never splits it.
+__device__ __forceinline__ bool mbar_wait_all(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* dev_status, int code) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, dev_status, code);
+  return __all_sync(0xffffffffu, ok);
 }
 
 // Warp-uniform bounded wait: lane 0 spins, the verdict is broadcast, then every lane
@@ -184,7 +208,6 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -216,9 +239,11 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int it = blockIdx.x; it < p.num_items && ok; it += gridDim.x) {
+        const WorkItem w = work_item(it, p.first_half_item);
         int m_blk, n_blk;
-        tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, m_blk, n_blk);
+        tile_coords(w.tile, p.num_m_blocks, p.num_n_blocks, p.group_m, m_blk, n_blk);
+        const int n0 = n_blk * BN + w.half * (BN / 2);
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -226,14 +251,30 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           uint8_t* sA = smem + stage * L::STAGE_BYTES;
           uint8_t* sB = sA + A_TILE_BYTES;
-          mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
-          tma_load_2d(sA, &tmA, &full_bar[stage], kb * BK, m_blk * BM);
-          if (B_KMAJOR) {
-            tma_load_2d(sB, &tmB, &full_bar[stage], kb * BK, n_blk * BN);
-          } else {
+          // (the two cases are spelled out so that the full tile's loads stay unrolled with
+          // constant offsets: this thread's issue rate is on the main loop's critical path)
+          if (!w.is_half) {
+            mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+            tma_load_2d(sA, &tmA, &full_bar[stage], kb * BK, m_blk * BM);
+            if (B_KMAJOR) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sB + j * (64 * BK * 2), &tmB, &full_bar[stage], n_blk * BN + j * 64, kb * BK);
+              for (int j = 0; j < BN / L::B_BOX_ROWS; ++j)
+                tma_load_2d(sB + j * (L::B_BOX_ROWS * BK * 2), &tmB, &full_bar[stage], kb * BK, n0 + j * L::B_BOX_ROWS);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sB + j * (64 * BK * 2), &tmB, &full_bar[stage], n0 + j * 64, kb * BK);
+            }
+          } else {
+            mbar_arrive_expect_tx(&full_bar[stage], A_TILE_BYTES + (BN / 2) * BK * 2);
+            tma_load_2d(sA, &tmA, &full_bar[stage], kb * BK, m_blk * BM);
+            if (B_KMAJOR) {
+              tma_load_2d(sB, &tmB, &full_bar[stage], kb * BK, n0);  // half tiles exist at BN = 256 only: one box
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 128; ++j)
+                tma_load_2d(sB + j * (64 * BK * 2), &tmB, &full_bar[stage], n0 + j * 64, kb * BK);
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -244,43 +285,51 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(UMMA_BF16, BM, BN, false, !B_KMAJOR);
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      int t = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
-        const int buf = SEGS > 1 ? 0 : (t & 1);
-        const uint32_t acc_phase = SEGS > 1 ? (t & 1u) : ((t >> 1) & 1u);
-        if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) break;
-        tc_fence_after_sync();
-        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-          const int seg = SEGS > 1 ? kb / p.seg_k_blocks : 0;
-          const int kb_in_seg = SEGS > 1 ? kb - seg * p.seg_k_blocks : kb;
-          const uint32_t d_tmem = tmem_base + (SEGS > 1 ? seg : buf) * BN;
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem + stage * L::STAGE_BYTES);
-          const uint32_t b_addr = a_addr + A_TILE_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t adesc = make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
-            const uint64_t bdesc = B_KMAJOR ? make_smem_desc_sw128(b_addr + k * 32, 16, 1024)
-                                            : make_smem_desc_sw128(b_addr + k * 2048, 64 * BK * 2, 1024);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb_in_seg | k) != 0 ? 1u : 0u);
-          }
-          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
-          }
+    // The whole warp walks the loop (waits included) and one elected lane issues: a lone
+    // divergent thread pays its address arithmetic per instruction, which bounds tiles of
+    // 128 columns and fewer (measured per k-block at 128 / 64 columns: 310 / 292 ns with one
+    // thread, 257 / 224 ns this way; 256-wide tiles are bound by the tensor pipe either way).
+    constexpr uint32_t idesc_full = make_idesc(UMMA_BF16, BM, BN, false, !B_KMAJOR);
+    constexpr uint32_t idesc_half = make_idesc(UMMA_BF16, BM, BN / 2, false, !B_KMAJOR);
+    // descriptors of stage 0; a stage / k step is an addition to the 16-byte-unit address field
+    const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
+    const uint64_t b_desc0 = B_KMAJOR ? make_smem_desc_sw128(smem_u32(smem) + A_TILE_BYTES, 16, 1024)
+                                      : make_smem_desc_sw128(smem_u32(smem) + A_TILE_BYTES, 64 * BK * 2, 1024);
+    constexpr uint64_t B_K_STEP = B_KMAJOR ? (32 >> 4) : (2048 >> 4);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int t = 0;
+    for (int it = blockIdx.x; it < p.num_items && ok; it += gridDim.x, ++t) {
+      const uint32_t idesc = it < p.first_half_item ? idesc_full : idesc_half;
+      const int buf = SEGS > 1 ? 0 : (t & 1);
+      const uint32_t acc_phase = SEGS > 1 ? (t & 1u) : ((t >> 1) & 1u);
+      if (!mbar_wait_all(&tmem_empty[buf], acc_phase ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) break;
+      tc_fence_after_sync();
+      for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+        const int seg = SEGS > 1 ? kb / p.seg_k_blocks : 0;
+        const int kb_in_seg = SEGS > 1 ? kb - seg * p.seg_k_blocks : kb;
+        const uint32_t d_tmem = tmem_base + (SEGS > 1 ? seg : buf) * BN;
+        if (!mbar_wait_all(&full_bar[stage], phase, abort_flag, p.dev_status, DEV_TIMEOUT_MMA)) {
+          ok = false;
+          break;
         }
-        if (ok) umma_commit(&tmem_full[buf]);
+        tc_fence_after_sync();
+        if (elect_one()) {
+          const uint64_t so = static_cast<uint64_t>((stage * L::STAGE_BYTES) >> 4);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_f16_ss(d_tmem, a_desc0 + so + static_cast<uint64_t>(k * 2), b_desc0 + so + k * B_K_STEP, idesc, (kb_in_seg | k) != 0 ? 1u : 0u);
+          umma_commit(&empty_bar[stage]);
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
+      if (ok && elect_one()) umma_commit(&tmem_full[buf]);
+      __syncwarp();
     }
   } else {
     // ---------------------------------------------------------------- epilogue
@@ -289,9 +338,10 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint8_t* stage_bufs = smem + L::STAGING_OFFSET + quarter * (2 * STAGING_BUF_BYTES);
     int sbuf = 0;
     int t = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+    for (int it = blockIdx.x; it < p.num_items; it += gridDim.x, ++t) {
+      const WorkItem w = work_item(it, p.first_half_item);
       int m_blk, n_blk;
-      tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, m_blk, n_blk);
+      tile_coords(w.tile, p.num_m_blocks, p.num_n_blocks, p.group_m, m_blk, n_blk);
       const int buf = SEGS > 1 ? 0 : (t & 1);
       const uint32_t acc_phase = SEGS > 1 ? (t & 1u) : ((t >> 1) & 1u);
       const int nseg = SEGS > 1 ? (p.num_k_blocks + p.seg_k_blocks - 1) / p.seg_k_blocks : 1;
@@ -304,8 +354,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
       // Output columns of this tile, one 128-byte row segment (CHUNK columns) at a time.
       constexpr int CHUNK = OUT_F32 ? 32 : 64;
-      const int out_cols = e.swiglu ? BN / 2 : BN;
-      const int out_col_base = n_blk * out_cols;
+      const int out_cols = (e.swiglu || w.is_half) ? BN / 2 : BN;
+      const int out_col_base = e.swiglu ? n_blk * (BN / 2) : n_blk * BN + w.half * (BN / 2);
       const int units = out_cols / CHUNK;
       // The tile's bias, 8 columns per lane, fetched once per tile with one coalesced load and
       // handed round by shuffles (a per-unit load by every lane of the same address costs an L2
@@ -475,7 +525,7 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int
   if (B_KMAJOR) {  // B(k,n) with unit k stride: a row-major (N,K) array
     const uint64_t dims[2] = {static_cast<uint64_t>(pr.K), static_cast<uint64_t>(pr.N)};
     const uint64_t strides[1] = {static_cast<uint64_t>(pr.sbn) * ab_size};
-    const uint32_t box[2] = {BK, BN};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(L::B_BOX_ROWS)};
     int rc = encode_tensor_map(ctx, &tmB, ab_dtype, 2, const_cast<void*>(pr.B), dims, strides, box, 1);
     if (rc) return rc;
   } else {  // B(k,n) with unit n stride: a row-major (K,N) array
@@ -519,6 +569,11 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int
   // this kernel's end; lh_b200_reserve_sms leaves them room.
   const int sms = ctx->sm_count - ctx->reserved_sms > 0 ? ctx->sm_count - ctx->reserved_sms : 1;
   const int grid = num_tiles < sms ? num_tiles : sms;
+  // the last partial wave as half tiles, when both halves of each of its tiles get an SM
+  const int leftover = num_tiles % grid;
+  const bool split_tail = BN == 256 && SEGS == 1 && !epi.swiglu && leftover > 0 && 2 * leftover <= grid;
+  p.first_half_item = split_tail ? num_tiles - leftover : num_tiles;
+  p.num_items = split_tail ? num_tiles + leftover : num_tiles;
   kernel<<<grid, NUM_THREADS, L::DYN_BYTES, ctx->stream>>>(tmA, tmB, tmD, p);
   LH_CHECK_LAUNCH(ctx, "gemm_bf16_tc_kernel");
   return LH_OK;

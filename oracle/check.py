@@ -58,7 +58,13 @@ def tolerance_for(dtype: str) -> float:
     return TOL_F32 if dtype in ("f32", "f64") else TOL_BF16
 
 
-def stack_scale(n_layer: int) -> float:
+LAYER_ROUNDINGS = 9            # bf16 roundings along one Llama layer on one device: normed x, q/k/v, rotary, P,
+                               # attention output, h = x + projection, normed h, SwiGLU output, h + down projection
+SHARDED_LAYER_ROUNDINGS = 13   # tensor parallel: each of the two contracting products also rounds every device's
+                               # partial sum and the reduced total before the residual add
+
+
+def stack_scale(n_layer: int, roundings_per_layer: int = LAYER_ROUNDINGS) -> float:
     """How the bounds grow with the depth of a decoder stack whose operators round to bf16.
 
     The stated 2e-2 bounds one chain of bf16 operators with f32 accumulation - one decoder layer
@@ -70,8 +76,13 @@ def stack_scale(n_layer: int) -> float:
     0.0064 * sqrt(layers) within 15 %, a third of the bound at every depth. For scale: two
     variants of this oracle that differ in one rounding per residual add are 0.0197 apart at
     8 layers, and the oracle is 0.019 from the f32 evaluation of the same model, so no bf16
-    implementation can be expected to stay within the one-layer bound at that depth."""
-    return max(1.0, float(n_layer) ** 0.5)
+    implementation can be expected to stay within the one-layer bound at that depth.
+
+    ``roundings_per_layer``: a schedule that rounds more often along a layer (the tensor-parallel
+    one: ``SHARDED_LAYER_ROUNDINGS`` against ``LAYER_ROUNDINGS``) is a longer chain by that ratio,
+    and the same quadrature applies: the scale is sqrt(n_layer * roundings / LAYER_ROUNDINGS).
+    Measured at 8 layers on 2, 4, 8 GPUs: 0.0233, 0.0244, 0.0244 against 0.0212 on one."""
+    return max(1.0, (float(n_layer) * roundings_per_layer / LAYER_ROUNDINGS) ** 0.5)
 
 
 def assert_close(out, ref, dtype: str, what: str = "") -> float:
@@ -81,12 +92,12 @@ def assert_close(out, ref, dtype: str, what: str = "") -> float:
     return err
 
 
-def assert_parity(out, ref, dtype: str, what: str = "", tol: float | None = None, n_layer: int = 1) -> float:
+def assert_parity(out, ref, dtype: str, what: str = "", tol: float | None = None, n_layer: int = 1, roundings_per_layer: int = LAYER_ROUNDINGS) -> float:
     """Both criteria. ``tol`` overrides the global bound only (a few f32 cases state a looser
     one with its reason); the per-element criterion always applies. ``n_layer`` > 1 scales
     both bounds for a deep stack (``stack_scale``); the small stacks of the parity tests do
     not use it."""
-    scale = stack_scale(n_layer)
+    scale = stack_scale(n_layer, roundings_per_layer)
     err = max_rel_err(out, ref)
     bound = (tolerance_for(dtype) if tol is None else tol) * scale
     assert err <= bound, f"{what}: max relative error {err:.3e} exceeds {bound:.1e} for {dtype}"
@@ -96,13 +107,15 @@ def assert_parity(out, ref, dtype: str, what: str = "", tol: float | None = None
     return err
 
 
-def parity_report(out, ref, dtype: str, n_layer: int = 1) -> dict:
+def parity_report(out, ref, dtype: str, n_layer: int = 1, roundings_per_layer: int = LAYER_ROUNDINGS) -> dict:
     """The two figures as a JSON-able record (bench.py prints it)."""
-    scale = stack_scale(n_layer)
+    scale = stack_scale(n_layer, roundings_per_layer)
     err = max_rel_err(out, ref)
     excess = elementwise_excess(out, ref, dtype) / scale
     tol = tolerance_for(dtype) * scale
     rec = {"max_rel_err": err, "tol": round(tol, 4), "elementwise_excess": excess, "ok": bool(err <= tol and excess <= 1.0)}
     if scale > 1.0:
         rec["tol_rule"] = f"{tolerance_for(dtype):g} per layer (one chain of bf16 operators) x sqrt({n_layer} layers): independent rounding errors of the layers add in quadrature"
+        if roundings_per_layer != LAYER_ROUNDINGS:
+            rec["tol_rule"] += f"; x sqrt({roundings_per_layer}/{LAYER_ROUNDINGS}): this schedule rounds {roundings_per_layer} times along a layer instead of {LAYER_ROUNDINGS}"
     return rec
