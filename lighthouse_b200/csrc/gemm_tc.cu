@@ -235,7 +235,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // (warp-uniform like the MMA issuer: every lane waits, one elected lane issues)
+    {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -245,7 +246,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tile_coords(w.tile, p.num_m_blocks, p.num_n_blocks, p.group_m, m_blk, n_blk);
         const int n0 = n_blk * BN + w.half * (BN / 2);
         for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_PRODUCER)) {
+          if (!mbar_wait_all(&empty_bar[stage], phase ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
           }
@@ -253,6 +254,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           uint8_t* sB = sA + A_TILE_BYTES;
           // (the two cases are spelled out so that the full tile's loads stay unrolled with
           // constant offsets: this thread's issue rate is on the main loop's critical path)
+          if (elect_one()) {
           if (!w.is_half) {
             mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
             tma_load_2d(sA, &tmA, &full_bar[stage], kb * BK, m_blk * BM);
@@ -276,6 +278,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 tma_load_2d(sB + j * (64 * BK * 2), &tmB, &full_bar[stage], n0 + j * 64, kb * BK);
             }
           }
+          }
+          __syncwarp();
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
