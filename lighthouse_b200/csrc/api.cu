@@ -211,6 +211,10 @@ extern "C" int lh_b200_ctx_destroy(lh_ctx_t* ctx) {
   for (void* ptr : ctx->retired_scratch) cudaFree(ptr);
   if (ctx->symm_counter) cudaFree(ctx->symm_counter);
   for (auto& t : ctx->rope_tables) cudaFree(t.data);
+  for (auto& pl : ctx->attn_plans) {
+    if (pl.table) cudaFree(pl.table);
+    if (pl.counters) cudaFree(pl.counters);
+  }
   if (ctx->rope_built) cudaEventDestroy(ctx->rope_built);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
   if (ctx->host_status) cudaFreeHost(ctx->host_status);
@@ -649,13 +653,20 @@ extern "C" int lh_b200_allgather(lh_ctx_t* ctx, const lh_memref_t* out, const lh
 namespace lh {
 // Upper bound of the context scratch an operator can ask for, from its operand views alone
 // (the choice between kernels also looks at pointer alignment, which is not known yet).
-size_t op_scratch_bytes(const lh_op_t& op) {
+size_t op_scratch_bytes(lh_ctx* ctx, const lh_op_t& op) {
   if (op.kind == LH_OP_ATTENTION) {
     const lh_view_t& q = op.operands[1];
     const lh_view_t& k = op.operands[2];
     if (q.slot < 0 || k.slot < 0 || q.rank < 3) return 0;
     const int64_t d = q.shape[q.rank - 1];
-    if (q.dtype == LH_BF16 && (d == 64 || d == 128)) return 0;  // tensor-core kernel: no score matrix
+    if (q.dtype == LH_BF16 && (d == 64 || d == 128)) {
+      // tensor-core kernel: no score matrix; partial results where a small causal grid is split
+      const int64_t heads = q.rank >= 3 ? q.shape[q.rank - 3] : 1;
+      const int64_t batch = q.rank >= 4 ? q.shape[0] : 1;
+      if (q.rank > 4 || batch * heads > 0x7fffffffLL) return 0;
+      return attn_tc_scratch_bytes(ctx, static_cast<int>(batch), static_cast<int>(heads), static_cast<int>(q.shape[q.rank - 2]),
+                                   static_cast<int>(k.shape[k.rank - 2]), static_cast<int>(d), op.i0);
+    }
     return static_cast<size_t>(q.shape[q.rank - 2]) * static_cast<size_t>(k.shape[k.rank - 2]) * sizeof(float);
   }
   if (op.kind == LH_OP_GEMM) {
@@ -703,7 +714,7 @@ extern "C" int lh_b200_module_create(lh_ctx_t* ctx, const char* entry_name, cons
   {
     size_t need = 0;
     for (int i = 0; i < nops; ++i) {
-      const size_t b = lh::op_scratch_bytes(ops[i]);
+      const size_t b = lh::op_scratch_bytes(ctx, ops[i]);
       if (b > need) need = b;
     }
     if (need) {

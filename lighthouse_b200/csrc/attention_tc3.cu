@@ -28,6 +28,9 @@
 #include "epilogue.cuh"
 #include "ptx.cuh"
 
+#include <algorithm>
+#include <vector>
+
 namespace lh {
 
 namespace {
@@ -45,8 +48,15 @@ struct Attn3Params {
   float scale_log2;
   int causal;
   int num_q_pairs;
-  int num_items;  // B * Hq * num_q_pairs
+  int num_items;  // B * Hq * num_q_pairs, or the length of `table`
   int* dev_status;
+  // Split key ranges (small causal grids, see AttnSplitPlan): work items come from a table,
+  // an item covers `chunk` key tiles of its pair of query tiles, and a tile whose key range is
+  // spread over several items is put together by whichever of them finishes last.
+  const int4* table;  // nullptr: items are whole pairs, numbered arithmetically
+  float* part;        // [(slot * 2 + tile) * max_chunks + chunk index] blocks of 128 x (HD + 4) floats: O unnormalised, m, l
+  int* counters;      // [slot * 2 + tile]: items of that tile finished so far (zero between launches)
+  int chunk, max_chunks;
 };
 
 template <int HD>
@@ -79,6 +89,9 @@ __device__ __forceinline__ bool wait_warp3(uint64_t* bar, uint32_t parity, volat
 // of its two query tiles visits (0 for a tile that lies outside the queries).
 struct Item3 {
   int b, hq, hkv, q0, n_a, n_b, n_max;
+  int j0;            // first key tile this item visits
+  int cidx, slot;    // split items: which chunk of the pair's key range, and the pair's slot in the partial buffers
+  int nch_a, nch_b;  // over how many items each tile's key range is spread (1: this item writes the result itself)
 };
 
 __device__ __forceinline__ int kv_tiles_for(const Attn3Params& p, int q0) {
@@ -108,20 +121,34 @@ __device__ __forceinline__ int item_of_round(int r, int cta, int grid, int num_i
 __device__ __forceinline__ Item3 decode_item(const Attn3Params& p, int item) {
   const int nbh = p.B * p.Hq;
   int bh, qp;
-  if (p.causal) {
+  Item3 w;
+  w.j0 = 0; w.cidx = 0; w.slot = -1; w.nch_a = 1; w.nch_b = 1;
+  if (p.table) {
+    const int4 e = __ldg(&p.table[item]);
+    bh = e.x;
+    qp = e.y & 0xffff;
+    w.cidx = e.y >> 16;
+    w.j0 = e.z;
+    w.slot = e.w;
+  } else if (p.causal) {
     qp = p.num_q_pairs - 1 - item / nbh;
     bh = item % nbh;
   } else {
     bh = item / p.num_q_pairs;
     qp = item % p.num_q_pairs;
   }
-  Item3 w;
   w.b = bh / p.Hq;
   w.hq = bh % p.Hq;
   w.hkv = w.hq / (p.Hq / p.Hkv);
   w.q0 = qp * (2 * BQ3);
   w.n_a = kv_tiles_for(p, w.q0);
   w.n_b = kv_tiles_for(p, w.q0 + BQ3);
+  if (p.table) {
+    w.nch_a = (w.n_a + p.chunk - 1) / p.chunk;
+    w.nch_b = (w.n_b + p.chunk - 1) / p.chunk;
+    w.n_a = min(max(w.n_a - w.j0, 0), p.chunk);
+    w.n_b = min(max(w.n_b - w.j0, 0), p.chunk);
+  }
   w.n_max = max(w.n_a, w.n_b);
   return w;
 }
@@ -148,6 +175,7 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* pv_done = bars + 16;  // [2] tiles
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* arrivals = abort_flag + 1;  // [2] tiles: how many items of a split tile had finished before this one
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -213,7 +241,7 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mbar_arrive_expect_tx(&k_full[st], L::KV_BYTES);
 #pragma unroll
           for (int h = 0; h < HD / 64; ++h)
-            tma_load_4d(smem + L::K_OFF + st * L::KV_BYTES + h * SUBTILE3, &tmK, &k_full[st], h * 64, j * BKV3, w.hkv, w.b);
+            tma_load_4d(smem + L::K_OFF + st * L::KV_BYTES + h * SUBTILE3, &tmK, &k_full[st], h * 64, (w.j0 + j) * BKV3, w.hkv, w.b);
           if (!mbar_wait(&v_empty[st], ph ^ 1u, abort_flag, p.dev_status, DEV_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
@@ -221,7 +249,7 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mbar_arrive_expect_tx(&v_full[st], L::KV_BYTES);
 #pragma unroll
           for (int h = 0; h < HD / 64; ++h)
-            tma_load_4d(smem + L::V_OFF + st * L::KV_BYTES + h * SUBTILE3, &tmV, &v_full[st], h * 64, j * BKV3, w.hkv, w.b);
+            tma_load_4d(smem + L::V_OFF + st * L::KV_BYTES + h * SUBTILE3, &tmV, &v_full[st], h * 64, (w.j0 + j) * BKV3, w.hkv, w.b);
         }
       }
     }
@@ -345,9 +373,15 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     bool ok = true;
     FOR_EACH_ITEM(item) {
       if (!ok) break;
-      const Item3 w = decode_item(p, item);
-      const int n_mine = t == 0 ? w.n_a : w.n_b;
-      const int q0t = w.q0 + t * BQ3;
+      // (only what the key loop needs stays live through it; the item is decoded again for the
+      // write-out, which keeps the loop free of spills)
+      int n_mine, q0t, key0;
+      {
+        const Item3 w = decode_item(p, item);
+        n_mine = t == 0 ? w.n_a : w.n_b;
+        q0t = w.q0 + t * BQ3;
+        key0 = w.j0 * BKV3;
+      }
       const int q_row = q0t + row;
       float m_used = -INFINITY;
       float l = 0.f;
@@ -357,7 +391,7 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           break;
         }
         tc_fence_after_sync();
-        const int col0 = j * BKV3;
+        const int col0 = key0 + j * BKV3;
         const bool need_mask = (col0 + BKV3 > p.Skv) || (p.causal && (col0 + BKV3 - 1 > q0t + offset));
         const int limit = need_mask ? (p.causal ? min(p.Skv - 1, q_row + offset) : (p.Skv - 1)) - col0 : BKV3;  // last visible column in this tile
         // pass 1: row max of the scores, two 32-column loads in flight at a time
@@ -454,21 +488,95 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           break;
         }
         tc_fence_after_sync();
-        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+        const Item3 w = decode_item(p, item);
         char* obase = static_cast<char*>(p.O);
         const int64_t oidx = static_cast<int64_t>(w.b) * p.sob + static_cast<int64_t>(w.hq) * p.soh + static_cast<int64_t>(q_row) * p.sos;
+        const int nch_mine = t == 0 ? w.nch_a : w.nch_b;
+        if (nch_mine <= 1) {
+          const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld_32x32b_x32(o_addr + c * 32, o);
-          tmem_ld_wait();
-          if (q_row < p.Sq) {
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(o_addr + c * 32, o);
+            tmem_ld_wait();
+            if (q_row < p.Sq) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              float v[8];
+              for (int g = 0; g < 4; ++g) {
+                float v[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(o[g * 8 + i]) * inv_l;
-              store8_from_f32(obase, p.o_dtype, oidx + c * 32 + g * 8, v);
+                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(o[g * 8 + i]) * inv_l;
+                store8_from_f32(obase, p.o_dtype, oidx + c * 32 + g * 8, v);
+              }
+            }
+          }
+        } else {
+          // This tile's keys are spread over nch_mine items. Every one of them leaves its
+          // un-normalised accumulator, reference maximum and row sum in global memory and counts
+          // itself in; the one that finds all the others counted puts the rows together:
+          // O = sum_c 2^(m_c - M) O_c / sum_c 2^(m_c - M) l_c with M = max_c m_c. Nobody waits.
+          // One item's block: [HD / 4 groups of 4 columns][128 rows][4] then m[128], l[128]: a
+          // warp's 32 rows of one group are 512 contiguous bytes, for the writes here and the
+          // reads of the merge alike (a row per thread with rows 528 bytes apart made each
+          // 16-byte access its own transaction: 25 us per item).
+          constexpr int BLOCK = BQ3 * (HD + 4);
+          float* tile_part = p.part + static_cast<int64_t>(w.slot * 2 + t) * p.max_chunks * BLOCK;
+          float* mine = tile_part + static_cast<int64_t>(w.cidx) * BLOCK;
+#pragma unroll
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(o_addr + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              __stcg(reinterpret_cast<uint4*>(mine) + (c * 8 + g) * BQ3 + row, make_uint4(o[4 * g], o[4 * g + 1], o[4 * g + 2], o[4 * g + 3]));
+          }
+          __stcg(mine + HD * BQ3 + row, m_used);
+          __stcg(mine + (HD + 1) * BQ3 + row, l);
+          __threadfence();
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");  // the tile's 128 rows are written
+          if (row == 0) arrivals[t] = atomicAdd(&p.counters[w.slot * 2 + t], 1);
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");
+          const bool last = arrivals[t] == nch_mine - 1;
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");  // everyone has read the verdict before the next item overwrites it
+          if (last) {
+            __threadfence();
+            if (row == 0) p.counters[w.slot * 2 + t] = 0;  // ready for the next launch
+            float M = -INFINITY;
+            for (int c = 0; c < nch_mine; ++c) M = fmaxf(M, __ldcg(tile_part + static_cast<int64_t>(c) * BLOCK + HD * BQ3 + row));
+            float L = 0.f;
+            for (int c = 0; c < nch_mine; ++c) {
+              const float* blk = tile_part + static_cast<int64_t>(c) * BLOCK;
+              const float mc = __ldcg(blk + HD * BQ3 + row), lc = __ldcg(blk + (HD + 1) * BQ3 + row);
+              L += (mc == -INFINITY) ? 0.f : ex2_approx(mc - M) * lc;
+            }
+            const float inv_l = (L > 0.f) ? 1.f / L : 0.f;
+            if (q_row < p.Sq) {
+#pragma unroll 1
+              for (int cb = 0; cb < HD / 32; ++cb) {
+                float acc[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+                for (int c = 0; c < nch_mine; ++c) {
+                  const float* blk = tile_part + static_cast<int64_t>(c) * BLOCK;
+                  const float mc = __ldcg(blk + HD * BQ3 + row);
+                  const float wgt = (mc == -INFINITY) ? 0.f : ex2_approx(mc - M);
+#pragma unroll
+                  for (int g = 0; g < 8; ++g) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(blk) + (cb * 8 + g) * BQ3 + row);
+                    acc[4 * g] = fmaf(wgt, v.x, acc[4 * g]);
+                    acc[4 * g + 1] = fmaf(wgt, v.y, acc[4 * g + 1]);
+                    acc[4 * g + 2] = fmaf(wgt, v.z, acc[4 * g + 2]);
+                    acc[4 * g + 3] = fmaf(wgt, v.w, acc[4 * g + 3]);
+                  }
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  float v[8];
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) v[i] = acc[g * 8 + i] * inv_l;
+                  store8_from_f32(obase, p.o_dtype, oidx + cb * 32 + g * 8, v);
+                }
+              }
             }
           }
         }
@@ -490,6 +598,87 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+// Key tiles a 128-row query tile starting at q0 visits (host copy of kv_tiles_for).
+int host_kv_tiles(int Sq, int Skv, int causal, int q0) {
+  if (q0 >= Sq) return 0;
+  int n = (Skv + BKV3 - 1) / BKV3;
+  if (causal) {
+    int last_col = q0 + BQ3 - 1 + (Skv - Sq);
+    if (last_col > Skv - 1) last_col = Skv - 1;
+    if (last_col < 0) last_col = 0;
+    const int m = last_col / BKV3 + 1;
+    if (m < n) n = m;
+  }
+  return n;
+}
+
+// The plan for this shape, built on first use. A causal grid is split when there are no more
+// pairs of query tiles than SMs - every SM then gets at most one pair and the heaviest pair
+// sets the time (8 sequences-times-heads of 4096 positions: 128 pairs on 148 SMs, the heaviest
+// 32 key tiles against a mean of 14.7 per SM: 77 us, 69 us with chunks of 8 key tiles, and
+// less with chunks of the mean load). An item costs about 10 us beyond its key tiles (pipeline
+// fill and drain, 134 KB of partial results written and read back), so grids with more pairs
+// than SMs, which snake order already balances to within a few key tiles, stay whole: split
+// they were measured 25-35 % slower. Items are `chunk` key tiles of a pair, chunk = the mean
+// load per SM rounded up to even, sorted heaviest first for the kernel's snake order.
+const AttnSplitPlan* split_plan(lh_ctx* ctx, int BH, int Sq, int Skv, int HD, int causal) {
+  const int pairs = (Sq + 2 * BQ3 - 1) / (2 * BQ3);
+  const int64_t whole_items = static_cast<int64_t>(BH) * pairs;
+  const int grid = whole_items < ctx->sm_count ? static_cast<int>(whole_items) : ctx->sm_count;
+  for (const AttnSplitPlan& pl : ctx->attn_plans)
+    if (pl.bh == BH && pl.sq == Sq && pl.skv == Skv && pl.hd == HD && pl.grid == grid) return pl.chunk ? &pl : nullptr;
+  AttnSplitPlan pl{};
+  pl.bh = BH; pl.sq = Sq; pl.skv = Skv; pl.hd = HD; pl.grid = grid;
+  std::vector<int> n_max(pairs);
+  int64_t work = 0;
+  int heaviest = 0;
+  for (int qp = 0; qp < pairs; ++qp) {
+    const int na = host_kv_tiles(Sq, Skv, causal, qp * 2 * BQ3), nb = host_kv_tiles(Sq, Skv, causal, qp * 2 * BQ3 + BQ3);
+    n_max[qp] = na > nb ? na : nb;
+    work += n_max[qp];
+    if (n_max[qp] > heaviest) heaviest = n_max[qp];
+  }
+  work *= BH;
+  const double mean = static_cast<double>(work) / ctx->sm_count;
+  if (causal && heaviest >= 8 && whole_items <= ctx->sm_count && heaviest > 1.25 * mean && pairs < 0x10000) {
+    int chunk = 2 * static_cast<int>((mean + 1.999) / 2.0);
+    chunk = chunk < 4 ? 4 : chunk > 16 ? 16 : chunk;
+    struct Entry { int size, bh, qp, c, j0, slot; };
+    std::vector<Entry> entries;
+    int slots = 0, max_chunks = 1;
+    for (int bh = 0; bh < BH; ++bh)
+      for (int qp = 0; qp < pairs; ++qp) {
+        const int nch = (n_max[qp] + chunk - 1) / chunk;
+        if (nch > max_chunks) max_chunks = nch;
+        const int slot = nch > 1 ? slots++ : -1;
+        for (int c = 0; c < nch; ++c) {
+          const int left = n_max[qp] - c * chunk;
+          entries.push_back({left < chunk ? left : chunk, bh, qp, c, c * chunk, slot});
+        }
+      }
+    std::stable_sort(entries.begin(), entries.end(), [](const Entry& x, const Entry& y) { return x.size > y.size; });
+    const size_t part_bytes = static_cast<size_t>(slots) * 2 * max_chunks * BQ3 * (HD + 4) * sizeof(float);
+    if (slots > 0 && part_bytes <= (512ull << 20)) {
+      std::vector<int4> table(entries.size());
+      for (size_t i = 0; i < entries.size(); ++i) table[i] = make_int4(entries[i].bh, entries[i].qp | (entries[i].c << 16), entries[i].j0, entries[i].slot);
+      void* dev_table = nullptr;
+      int* dev_counters = nullptr;
+      if (cudaMalloc(&dev_table, table.size() * sizeof(int4)) == cudaSuccess && cudaMalloc(&dev_counters, static_cast<size_t>(slots) * 2 * sizeof(int)) == cudaSuccess &&
+          cudaMemcpy(dev_table, table.data(), table.size() * sizeof(int4), cudaMemcpyHostToDevice) == cudaSuccess &&
+          cudaMemset(dev_counters, 0, static_cast<size_t>(slots) * 2 * sizeof(int)) == cudaSuccess) {
+        pl.chunk = chunk; pl.max_chunks = max_chunks; pl.n_items = static_cast<int>(entries.size()); pl.n_slots = slots;
+        pl.table = dev_table; pl.counters = dev_counters; pl.part_bytes = part_bytes;
+      } else {
+        cudaGetLastError();  // no table: the shape runs as whole pairs
+        if (dev_table) cudaFree(dev_table);
+        if (dev_counters) cudaFree(dev_counters);
+      }
+    }
+  }
+  ctx->attn_plans.push_back(pl);
+  return ctx->attn_plans.back().chunk ? &ctx->attn_plans.back() : nullptr;
 }
 
 template <int HD>
@@ -518,7 +707,18 @@ int launch3_hd(lh_ctx* ctx, const AttnProblem& a) {
   p.scale_log2 = a.scale * 1.44269504088896340736f;
   p.causal = a.causal;
   p.num_q_pairs = (a.Sq + 2 * BQ3 - 1) / (2 * BQ3);
-  const int64_t items = static_cast<int64_t>(a.B) * a.Hq * p.num_q_pairs;
+  int64_t items = static_cast<int64_t>(a.B) * a.Hq * p.num_q_pairs;
+  p.table = nullptr; p.part = nullptr; p.counters = nullptr; p.chunk = 0; p.max_chunks = 1;
+  if (const AttnSplitPlan* pl = split_plan(ctx, a.B * a.Hq, a.Sq, a.Skv, HD, a.causal)) {
+    int rc = ensure_scratch(ctx, pl->part_bytes);
+    if (rc) return rc;
+    p.table = static_cast<const int4*>(pl->table);
+    p.part = static_cast<float*>(ctx->scratch);
+    p.counters = pl->counters;
+    p.chunk = pl->chunk;
+    p.max_chunks = pl->max_chunks;
+    items = pl->n_items;
+  }
   p.num_items = static_cast<int>(items);
   p.dev_status = ctx->dev_status;
   auto kernel = attn_fwd_tc3_kernel<HD>;
@@ -530,6 +730,12 @@ int launch3_hd(lh_ctx* ctx, const AttnProblem& a) {
 }
 
 }  // namespace
+
+size_t attn_tc_scratch_bytes(lh_ctx* ctx, int B, int Hq, int Sq, int Skv, int D, int causal) {
+  if (ctx->cc_major != 10 || (D != 64 && D != 128) || Sq <= BQ3 || B < 1 || Hq < 1) return 0;
+  const AttnSplitPlan* pl = split_plan(ctx, B * Hq, Sq, Skv, D, causal);
+  return pl ? pl->part_bytes : 0;
+}
 
 int attn_tc3_launch(lh_ctx* ctx, const AttnProblem& a) {
   if (a.scale <= 0.f) return set_error(ctx, LH_ERR_UNSUPPORTED, "attention: scale must be positive");

@@ -25,6 +25,18 @@ struct SymmRegion {
   char* peers[LH_MAX_RANKS];
 };
 
+// How a small causal attention grid is cut into work items whose key ranges are parts of a
+// pair of query tiles' range (attention_tc3.cu). Built once per problem shape, kept until the
+// context goes.
+struct AttnSplitPlan {
+  int bh, sq, skv, hd, grid;  // the shape it was built for
+  int chunk;                  // key tiles per item; 0: this shape is not split
+  int max_chunks, n_items, n_slots;
+  void* table;                // device, n_items x int4
+  int* counters;              // device, n_slots x 2, zero between launches
+  size_t part_bytes;          // partial results in the context's scratch
+};
+
 struct lh_ctx {
   int device = 0;
   int sm_count = 0;
@@ -63,6 +75,7 @@ struct lh_ctx {
   struct RopeTable { float theta; int dim, positions; float* data; };  // (cos, sin) of positions [0, positions)
   std::vector<RopeTable> rope_tables;
   cudaEvent_t rope_built = nullptr;   // orders a table's build before the other stream's later work
+  std::vector<AttnSplitPlan> attn_plans;
 };
 
 namespace lh {
@@ -169,6 +182,9 @@ int attn_tc_supported(const lh_ctx* ctx, const AttnProblem& p);
 int attn_tc_launch(lh_ctx* ctx, const AttnProblem& p);
 int attn_tc2_launch(lh_ctx* ctx, const AttnProblem& p);
 int attn_tc3_launch(lh_ctx* ctx, const AttnProblem& p);
+// Scratch the tensor-core attention needs for this shape (0 unless its key ranges are split);
+// builds and uploads the shape's work-item table on first use (allocates: not under capture).
+size_t attn_tc_scratch_bytes(lh_ctx* ctx, int B, int Hq, int Sq, int Skv, int D, int causal);
 int attn_simt_launch(lh_ctx* ctx, const AttnProblem& p);
 
 // ------------------------------------------------------------ row operators

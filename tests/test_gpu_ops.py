@@ -241,6 +241,27 @@ def test_attention_config3_full_size_properties(ctx):
         assert bool(torch.isfinite(o.float()).all())
 
 
+@pytest.mark.parametrize("shape,out", [((1, 2, 2, 4096, 4096, 128), "bf16"), ((1, 4, 2, 2048, 2048, 128), "f32"), ((1, 3, 3, 1000, 1300, 64), "bf16"), ((2, 4, 1, 3000, 3000, 128), "bf16")])
+def test_attention_causal_small_grid_splits_key_ranges(ctx, shape, out):
+    """Causal problems with few (batch, head) pairs and long rows: the kernel spreads a pair of
+    query tiles' key range over several work items and the last one to finish merges the
+    partial (O, m, l). Same oracle and bound as the un-split kernel; a second call must give
+    the same bits (the arrival counters are back at zero, the merge order does not depend on
+    which item came last)."""
+    b, hq, hkv, sq, skv, d = shape
+    q, k, v = I.attention_qkv(b, hq, hkv, sq, skv, d, seed=sq + hq)
+    ref = R.attention(I.to_np(q), I.to_np(k), I.to_np(v), causal=True, io_dtype="bf16")  # an f32 result only lacks the last rounding
+    qd, kd, vd = dev(q), dev(k), dev(v)
+    o = torch.full((b, hq, sq, d), 5.0, device="cuda", dtype=torch.bfloat16 if out == "bf16" else torch.float32)
+    ctx.attention_fwd(o, qd, kd, vd, d**-0.5, True)
+    ctx.sync()
+    assert_parity(host(o), ref, "bf16")
+    o2 = torch.zeros_like(o)
+    ctx.attention_fwd(o2, qd, kd, vd, d**-0.5, True)
+    ctx.sync()
+    assert torch.equal(o, o2)
+
+
 # ----------------------------------------------------------------------------------- row kernels
 @pytest.mark.parametrize("rows,n,xdt,odt", [(1000, 768, "f32", "bf16"), (64, 768, "f32", "f32"), (33, 100, "f32", "f32"), (17, 4096, "bf16", "bf16"), (5, 5000, "f32", "f32")])
 def test_layernorm(ctx, rows, n, xdt, odt):
