@@ -287,10 +287,13 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
                 fused = False
             else:
                 weights += symm_args
-        plan = D.build_llama_plan_overlapped(cfg, tp_rank, tp, args.microbatches, args.reserve_sms, fused=fused) if overlapped else D.build_llama_plan(cfg, tp_rank, tp)
+        # with the fused kernel the result buffers are symmetric memory too: the last layer's
+        # kernel gathers straight into them (every rank holds the whole result either way)
+        plan = D.build_llama_plan_overlapped(cfg, tp_rank, tp, args.microbatches, args.reserve_sms, fused=fused, result_symmetric=fused) if overlapped else D.build_llama_plan(cfg, tp_rank, tp)
         host_in = torch.randn(cfg.tokens, cfg.dim, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).pin_memory()
         dev_in = host_in.cuda()
-        dev_out = torch.empty(cfg.tokens, cfg.dim, device="cuda", dtype=torch.bfloat16)
+        new_result = (lambda: symm.empty((cfg.tokens, cfg.dim), torch.bfloat16)) if fused else (lambda: torch.empty(cfg.tokens, cfg.dim, device="cuda", dtype=torch.bfloat16))
+        dev_out = new_result()
     else:
         w = I.nanogpt_weights(cfg.n_layer, cfg.n_embd, cfg.hidden, cfg.vocab, cfg.block_size, seed=4)
         # nanoGPT has no fused collective kernel (LayerNorm, f32 residual); its overlapped schedule
@@ -337,7 +340,7 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
         # Steps are pipelined the way a serving loop would: two input and two result buffers, the
         # copy of step i+1's input and the read-back of step i-1's result run on copy streams
         # under step i's kernels. Every step still moves its own input and its own result.
-        dev_in2, dev_out2 = torch.empty_like(dev_in), torch.empty_like(dev_out)
+        dev_in2, dev_out2 = torch.empty_like(dev_in), (new_result() if which == "llama" else torch.empty_like(dev_out))
         bufs = [(dev_in, dev_out, dev_args), (dev_in2, dev_out2, [dev_out2, dev_in2] + weights)]
         h2d_stream, d2h_stream = torch.cuda.Stream(), torch.cuda.Stream()
         ev_in = [torch.cuda.Event() for _ in range(2)]

@@ -713,10 +713,15 @@ extern "C" int lh_b200_module_create(lh_ctx_t* ctx, const char* entry_name, cons
   // scratch the operators will ask for, allocated now instead of in the middle of a run
   {
     size_t need = 0;
+    const int reserved_now = ctx->reserved_sms;
     for (int i = 0; i < nops; ++i) {
+      // persistent kernels size their work lists by the SMs they may take: follow the plan's
+      // own reservations while sizing
+      if (ops[i].kind == LH_OP_RESERVE_SMS) ctx->reserved_sms = ops[i].i0 > 0 && ops[i].i0 < ctx->sm_count ? ops[i].i0 : 0;
       const size_t b = lh::op_scratch_bytes(ctx, ops[i]);
       if (b > need) need = b;
     }
+    ctx->reserved_sms = reserved_now;
     if (need) {
       int rc = ensure_scratch(ctx, need);
       if (rc) return rc;

@@ -623,10 +623,16 @@ int host_kv_tiles(int Sq, int Skv, int causal, int q0) {
 // than SMs, which snake order already balances to within a few key tiles, stay whole: split
 // they were measured 25-35 % slower. Items are `chunk` key tiles of a pair, chunk = the mean
 // load per SM rounded up to even, sorted heaviest first for the kernel's snake order.
+// SMs this kernel's persistent grid may take: like the GEMM it leaves the reserved ones to a
+// collective running beside it (a CTA that found its SM taken would start when another
+// finished, and its items with it).
+inline int usable_sms(const lh_ctx* ctx) { return ctx->sm_count - ctx->reserved_sms > 0 ? ctx->sm_count - ctx->reserved_sms : 1; }
+
 const AttnSplitPlan* split_plan(lh_ctx* ctx, int BH, int Sq, int Skv, int HD, int causal) {
   const int pairs = (Sq + 2 * BQ3 - 1) / (2 * BQ3);
   const int64_t whole_items = static_cast<int64_t>(BH) * pairs;
-  const int grid = whole_items < ctx->sm_count ? static_cast<int>(whole_items) : ctx->sm_count;
+  const int sms = usable_sms(ctx);
+  const int grid = whole_items < sms ? static_cast<int>(whole_items) : sms;
   for (const AttnSplitPlan& pl : ctx->attn_plans)
     if (pl.bh == BH && pl.sq == Sq && pl.skv == Skv && pl.hd == HD && pl.grid == grid) return pl.chunk ? &pl : nullptr;
   AttnSplitPlan pl{};
@@ -641,8 +647,8 @@ const AttnSplitPlan* split_plan(lh_ctx* ctx, int BH, int Sq, int Skv, int HD, in
     if (n_max[qp] > heaviest) heaviest = n_max[qp];
   }
   work *= BH;
-  const double mean = static_cast<double>(work) / ctx->sm_count;
-  if (causal && heaviest >= 8 && whole_items <= ctx->sm_count && heaviest > 1.25 * mean && pairs < 0x10000) {
+  const double mean = static_cast<double>(work) / sms;
+  if (causal && heaviest >= 8 && whole_items <= sms && heaviest > 1.25 * mean && pairs < 0x10000) {
     int chunk = 2 * static_cast<int>((mean + 1.999) / 2.0);
     chunk = chunk < 4 ? 4 : chunk > 16 ? 16 : chunk;
     struct Entry { int size, bh, qp, c, j0, slot; };
@@ -723,7 +729,7 @@ int launch3_hd(lh_ctx* ctx, const AttnProblem& a) {
   p.dev_status = ctx->dev_status;
   auto kernel = attn_fwd_tc3_kernel<HD>;
   LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
-  const int grid = items < ctx->sm_count ? static_cast<int>(items) : ctx->sm_count;  // one persistent CTA per SM
+  const int grid = items < usable_sms(ctx) ? static_cast<int>(items) : usable_sms(ctx);  // one persistent CTA per SM
   kernel<<<static_cast<unsigned>(grid), ATT3_THREADS, L::DYN_BYTES, ctx->stream>>>(tmQ, tmK, tmV, p);
   LH_CHECK_LAUNCH(ctx, "attn_fwd_tc3_kernel");
   return LH_OK;

@@ -396,7 +396,7 @@ def check_overlap(tokens: int, batch: int, tp: int, microbatches: int) -> None:
 
 
 def build_llama_plan_overlapped(cfg: LlamaConfig, rank: int, tp: int, microbatches: int = 2, reserve_sms: int = 16,
-                                name: str = "llama_forward", fused: bool = False) -> Plan:
+                                name: str = "llama_forward", fused: bool = False, result_symmetric: bool = False) -> Plan:
     """Same arguments and result as ``build_llama_plan``; different schedule for ``tp`` > 1.
 
     The all-reduce after each contraction is split into reduce-scatter + all-gather with the
@@ -409,7 +409,10 @@ def build_llama_plan_overlapped(cfg: LlamaConfig, rank: int, tp: int, microbatch
     multicast memory (``lh_b200_reduce_norm_gather``) instead of two NCCL calls around two
     row kernels. The partial-sum and gathered-activation buffers are then symmetric memory
     the caller allocates: ``2 * microbatches`` extra arguments after ``norm``, per micro-batch
-    ``part (tokens/microbatches, dim)`` then ``xn`` (same shape), see ``llama_symmetric_args``."""
+    ``part (tokens/microbatches, dim)`` then ``xn`` (same shape), see ``llama_symmetric_args``.
+    ``result_symmetric`` (fused only): the caller's result buffer is symmetric memory registered
+    with the context too, so the last layer's kernel gathers straight into it; otherwise the
+    gathered rows are copied there from ``xn``."""
     check_tp(cfg, tp)
     check_overlap(cfg.tokens, cfg.batch, tp, microbatches)
     d, t, hd = cfg.dim, cfg.tokens, cfg.head_dim
@@ -450,6 +453,9 @@ def build_llama_plan_overlapped(cfg: LlamaConfig, rank: int, tp: int, microbatch
         stream,) normalise those rows into their place in the gathered buffer (the result
         argument itself after the last layer) and gather."""
         if fused:
+            if last and result_symmetric:
+                p.reduce_norm_gather(p.arg(0).slice(0, mb * tm, tm), part[mb] if reduce else None, h[mb], weight, cfg.eps)
+                return
             p.reduce_norm_gather(xn[mb], part[mb] if reduce else None, h[mb], weight, cfg.eps)
             if last:
                 p.elementwise("copy", p.arg(0).slice(0, mb * tm, tm), xn[mb])

@@ -43,8 +43,8 @@ def run_gpt_rank(cfg, w, ids, rank, tp, allreduce=None, overlapped=False):
     return CpuPlanRunner(plan, allreduce, rank, tp).run(args)[0]
 
 
-def run_llama_rank(cfg, w, x, rank, tp, allreduce=None, overlapped=False, fused=False):
-    plan = D.build_llama_plan_overlapped(cfg, rank, tp, microbatches=2, fused=fused) if overlapped else D.build_llama_plan(cfg, rank, tp)
+def run_llama_rank(cfg, w, x, rank, tp, allreduce=None, overlapped=False, fused=False, result_symmetric=False):
+    plan = D.build_llama_plan_overlapped(cfg, rank, tp, microbatches=2, fused=fused, result_symmetric=result_symmetric) if overlapped else D.build_llama_plan(cfg, rank, tp)
     sw = D.shard_llama_weights(w, cfg, rank, tp)
     args = [np.zeros((cfg.tokens, cfg.dim), np.float32), I.to_np(x)] + [I.to_np(t) for t in D.flatten_llama_args(sw)]
     if fused:
@@ -134,7 +134,7 @@ def _tp_worker(rank, world, port, q):
         lw, x = llama_inputs(LLAMA)
         hidden = run_llama_rank(LLAMA, lw, x, rank, world, allreduce)
         hidden_overlapped = run_llama_rank(LLAMA, lw, x, rank, world, allreduce, overlapped=True)
-        hidden_fused = run_llama_rank(LLAMA, lw, x, rank, world, allreduce, overlapped=True, fused=True)
+        hidden_fused = run_llama_rank(LLAMA, lw, x, rank, world, allreduce, overlapped=True, fused=True, result_symmetric=True)
         q.put((rank, logits, hidden, hidden_overlapped, hidden_fused, logits_overlapped, logits_dp))
     finally:
         dist.destroy_process_group()
@@ -196,7 +196,12 @@ def test_overlapped_schedule_is_the_same_computation_and_is_fully_ordered():
     fused = D.build_llama_plan_overlapped(LLAMA, 0, 1, microbatches=2, fused=True)
     assert fused.kinds().count("reduce_norm_gather") == n_sub + 2 and "reducescatter" not in fused.kinds()
     assert len(fused.args) == len(plan.args) + 4 and fused.args[-1].name == "xn1"
-    assert max_rel_err(run_llama_rank(LLAMA, w, x, 0, 1, overlapped=True, fused=True), plain) < 2e-2
+    got = run_llama_rank(LLAMA, w, x, 0, 1, overlapped=True, fused=True)
+    assert max_rel_err(got, plain) < 2e-2
+    # with a symmetric result buffer the last layer gathers straight into it: no copy, same values
+    direct = D.build_llama_plan_overlapped(LLAMA, 0, 1, microbatches=2, fused=True, result_symmetric=True)
+    assert direct.kinds().count("reduce_norm_gather") == n_sub + 2 and direct.kinds().count("ew:copy") == fused.kinds().count("ew:copy") - 2
+    assert np.array_equal(run_llama_rank(LLAMA, w, x, 0, 1, overlapped=True, fused=True, result_symmetric=True), got)
 
 
 def test_nanogpt_overlapped_schedule_single_rank_and_limits():
