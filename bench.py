@@ -503,8 +503,8 @@ def kernel_gemm(ctx, peaks, source, K=4096, steps=20, warmup=5) -> dict:
 def kernel_gemm_f32(ctx, peaks, source, steps=20, warmup=5) -> dict:
     """f32 GEMM accumulating into C, M = N = K = 1024, A, B ~ U(-1, 1) (config 1): the lh-run
     matmul. Runs as six bf16 products on the tensor cores (one operand-split launch + one
-    tcgen05 GEMM over 6K with four accumulators per tile); the flop count is the f32 problem's
-    2MNK."""
+    tcgen05 GEMM whose stages hold the three bf16 terms of both operands, four accumulators per
+    tile); the flop count is the f32 problem's 2MNK."""
     import torch
 
     from lighthouse_b200.plan import ArgSpec, Plan

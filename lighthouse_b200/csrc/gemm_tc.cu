@@ -50,11 +50,13 @@ __host__ __device__ constexpr int tmem_cols_for(int bn) {
   return (2 * bn <= 32) ? 32 : (2 * bn <= 64) ? 64 : (2 * bn <= 128) ? 128 : (2 * bn <= 256) ? 256 : 512;
 }
 
-template <int BN, int STAGES>
+// TERMS = 3 (the split-f32 path): a stage holds three A tiles and three B tiles, the bf16
+// terms of the f32 operands' k-block.
+template <int BN, int STAGES, int TERMS = 1>
 struct SmemLayout {
   static constexpr int B_TILE_BYTES = BN * BK * 2;
   static constexpr int B_BOX_ROWS = BN == 256 ? 128 : BN;  // k-major B: rows per TMA box (a half tile is one box of the widest tile)
-  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+  static constexpr int STAGE_BYTES = TERMS * (A_TILE_BYTES + B_TILE_BYTES);
   static constexpr int STAGING_OFFSET = STAGES * STAGE_BYTES;  // multiple of 1024
   static constexpr int BAR_OFFSET = STAGING_OFFSET + STAGING_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4;
@@ -189,11 +191,12 @@ __device__ __forceinline__ void load_row_segment(uint4 (&seg)[8], const void* ba
 // in its own accumulator (SEGS * BN columns of tensor memory, no double buffering across tiles)
 // and the segments' sums are added with correctly rounded f32 adds in the epilogue: the tensor
 // core adds into an accumulator with truncation, which biases long sums.
-template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, int SEGS = 1>
+template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, int SEGS = 1, int TERMS = 1>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmD, const GemmTcParams p) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, TERMS>;
+  static_assert(TERMS == 1 || (TERMS == 3 && B_KMAJOR && SEGS > 1), "three-term stages are the split-f32 path's");
   constexpr int TMEM_COLS = SEGS > 1 ? tmem_cols_for((SEGS * BN + 1) / 2) : tmem_cols_for(BN);
   static_assert(SEGS == 1 || (B_KMAJOR && OUT_F32 && SEGS * BN <= 512), "segmented accumulation is the split-f32 path's");
   extern __shared__ uint8_t smem_raw[];
@@ -251,10 +254,20 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             break;
           }
           uint8_t* sA = smem + stage * L::STAGE_BYTES;
-          uint8_t* sB = sA + A_TILE_BYTES;
+          uint8_t* sB = sA + TERMS * A_TILE_BYTES;
           // (the two cases are spelled out so that the full tile's loads stay unrolled with
           // constant offsets: this thread's issue rate is on the main loop's critical path)
-          if (elect_one()) {
+          if (TERMS == 3) {
+            // tensor maps (k, row, term): term t of the k-block into tile t of the stage
+            if (elect_one()) {
+              mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+#pragma unroll
+              for (int t = 0; t < 3; ++t) {
+                tma_load_3d(sA + t * A_TILE_BYTES, &tmA, &full_bar[stage], kb * BK, m_blk * BM, t);
+                tma_load_3d(sB + t * L::B_TILE_BYTES, &tmB, &full_bar[stage], kb * BK, n0, t);
+              }
+            }
+          } else if (elect_one()) {
           if (!w.is_half) {
             mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
             tma_load_2d(sA, &tmA, &full_bar[stage], kb * BK, m_blk * BM);
@@ -297,7 +310,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     constexpr uint32_t idesc_half = make_idesc(UMMA_BF16, BM, BN / 2, false, !B_KMAJOR);
     // descriptors of stage 0; a stage / k step is an addition to the 16-byte-unit address field
     const uint64_t a_desc0 = make_smem_desc_sw128(smem_u32(smem), 16, 1024);
-    const uint64_t b_desc0 = B_KMAJOR ? make_smem_desc_sw128(smem_u32(smem) + A_TILE_BYTES, 16, 1024)
+    const uint64_t b_desc0 = B_KMAJOR ? make_smem_desc_sw128(smem_u32(smem) + TERMS * A_TILE_BYTES, 16, 1024)
                                       : make_smem_desc_sw128(smem_u32(smem) + A_TILE_BYTES, 64 * BK * 2, 1024);
     constexpr uint64_t B_K_STEP = B_KMAJOR ? (32 >> 4) : (2048 >> 4);
     int stage = 0;
@@ -321,9 +334,22 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tc_fence_after_sync();
         if (elect_one()) {
           const uint64_t so = static_cast<uint64_t>((stage * L::STAGE_BYTES) >> 4);
+          if (TERMS == 3) {
+            // x = h + m + l per operand: the six products of weight >= 2^-16, smallest first
+            constexpr int TA[6] = {0, 2, 1, 0, 1, 0}, TB[6] = {2, 0, 1, 1, 0, 0};
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_f16_ss(d_tmem, a_desc0 + so + static_cast<uint64_t>(k * 2), b_desc0 + so + k * B_K_STEP, idesc, (kb_in_seg | k) != 0 ? 1u : 0u);
+            for (int q = 0; q < 6; ++q) {
+              const uint64_t ad = a_desc0 + so + static_cast<uint64_t>((TA[q] * A_TILE_BYTES) >> 4);
+              const uint64_t bd = b_desc0 + so + static_cast<uint64_t>((TB[q] * L::B_TILE_BYTES) >> 4);
+#pragma unroll
+              for (int k = 0; k < BK / 16; ++k)
+                umma_f16_ss(d_tmem, ad + static_cast<uint64_t>(k * 2), bd + static_cast<uint64_t>(k * 2), idesc, (kb_in_seg | q | k) != 0 ? 1u : 0u);
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)
+              umma_f16_ss(d_tmem, a_desc0 + so + static_cast<uint64_t>(k * 2), b_desc0 + so + k * B_K_STEP, idesc, (kb_in_seg | k) != 0 ? 1u : 0u);
+          }
           umma_commit(&empty_bar[stage]);
         }
         __syncwarp();
@@ -512,21 +538,36 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
-template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, int SEGS = 1>
-int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int seg_k_blocks = 0) {
-  using L = SmemLayout<BN, STAGES>;
+// TERMS = 3: pr.A / pr.B point at three consecutive (rows, ld) bf16 arrays, the terms of the f32
+// operands, `term_stride_a` / `term_stride_b` elements apart; pr.K is the f32 operands' k range.
+template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, int SEGS = 1, int TERMS = 1>
+int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int seg_k_blocks = 0, int64_t term_stride_a = 0,
+                   int64_t term_stride_b = 0) {
+  using L = SmemLayout<BN, STAGES, TERMS>;
   CUtensorMap tmA, tmB, tmD;
   const int n_out = epi.swiglu ? pr.N / 2 : pr.N;
   constexpr uint64_t ab_size = 2;
   constexpr int ab_dtype = LH_BF16;
-  {
+  if (TERMS == 3) {
+    const uint64_t dims_a[3] = {static_cast<uint64_t>(pr.K), static_cast<uint64_t>(pr.M), 3};
+    const uint64_t strides_a[2] = {static_cast<uint64_t>(pr.sam) * ab_size, static_cast<uint64_t>(term_stride_a) * ab_size};
+    const uint32_t box_a[3] = {BK, BM, 1};
+    int rc = encode_tensor_map(ctx, &tmA, ab_dtype, 3, const_cast<void*>(pr.A), dims_a, strides_a, box_a, 1);
+    if (rc) return rc;
+    const uint64_t dims_b[3] = {static_cast<uint64_t>(pr.K), static_cast<uint64_t>(pr.N), 3};
+    const uint64_t strides_b[2] = {static_cast<uint64_t>(pr.sbn) * ab_size, static_cast<uint64_t>(term_stride_b) * ab_size};
+    const uint32_t box_b[3] = {BK, BN, 1};
+    rc = encode_tensor_map(ctx, &tmB, ab_dtype, 3, const_cast<void*>(pr.B), dims_b, strides_b, box_b, 1);
+    if (rc) return rc;
+  } else {
     const uint64_t dims[2] = {static_cast<uint64_t>(pr.K), static_cast<uint64_t>(pr.M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(pr.sam) * ab_size};
     const uint32_t box[2] = {BK, BM};
     int rc = encode_tensor_map(ctx, &tmA, ab_dtype, 2, const_cast<void*>(pr.A), dims, strides, box, 1);
     if (rc) return rc;
   }
-  if (B_KMAJOR) {  // B(k,n) with unit k stride: a row-major (N,K) array
+  if (TERMS == 3) {
+  } else if (B_KMAJOR) {  // B(k,n) with unit k stride: a row-major (N,K) array
     const uint64_t dims[2] = {static_cast<uint64_t>(pr.K), static_cast<uint64_t>(pr.N)};
     const uint64_t strides[1] = {static_cast<uint64_t>(pr.sbn) * ab_size};
     const uint32_t box[2] = {BK, static_cast<uint32_t>(L::B_BOX_ROWS)};
@@ -566,7 +607,7 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int
   p.epi = epi;
   p.seg_k_blocks = seg_k_blocks > 0 ? seg_k_blocks : p.num_k_blocks;
   p.dev_status = ctx->dev_status;
-  auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES, OUT_F32, SEGS>;
+  auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES, OUT_F32, SEGS, TERMS>;
   LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
   // A persistent grid that fills the GPU would make side-stream kernels (collectives) wait for
@@ -677,37 +718,33 @@ int gemm_tc_bf16_launch(lh_ctx* ctx, const GemmProblem& p) {
 // h = bf16(x), m = bf16(x - h), l = bf16(x - h - m) (both differences are exact in f32). The
 // f32 product is summed from the six bf16 products whose weight is at least 2^-16,
 //   h*h + h*m + m*h + m*m + h*l + l*h     (dropped: m*l, l*m, l*l, about 2^-24 relative),
-// with f32 accumulation in tensor memory. The six products are one bf16 GEMM over a
-// concatenated k dimension,
-//   A' (M, 6K) = [A_h | A_h | A_m | A_m | A_h | A_l],   B' (N, 6K) = [B_h | B_m | B_h | B_m | B_l | B_h]
-// (both k-major), written by split_bf16x3_kernel into context scratch (which also transposes
-// B as needed). Against three tf32 products of a (head, remainder) split the operand bytes are
-// the same and the instruction count too, but a bf16 instruction covers twice the k.
+// with f32 accumulation in tensor memory. split_bf16x3_kernel writes the terms of both operands
+// as three k-major bf16 arrays each into context scratch (transposing B as needed): 6 bytes per
+// operand element. The GEMM kernel's three-term instantiation loads the three A tiles and three
+// B tiles of a k-block into one stage and issues the six products from them - the operand
+// bytes into the SM, which bound this path, are half of what one concatenated [h h m m h l] x
+// [h m h m l h] k dimension would move, and a quarter of the barrier rounds.
 // The tensor core adds into its f32 accumulator with truncation, a bias towards zero of about
-// 3e-8 of the sum per instruction. So k is cut into segments of SPLIT_SEGMENT original columns
-// (96 instructions), each summed in its own accumulator, and the segments' sums are added with
-// correctly rounded f32 adds in the epilogue; the concatenation above is per segment. A k range
-// beyond what one launch's accumulators hold takes further launches whose epilogue adds the
-// running result as C.
+// 3e-8 of the sum per instruction. So k is cut into segments of SPLIT_SEGMENT columns (96
+// instructions), each summed in its own accumulator, and the segments' sums are added with
+// correctly rounded f32 adds in the epilogue. A k range beyond what one launch's accumulators
+// hold takes further launches whose epilogue adds the running result as C.
 namespace {
 
 struct SplitOperand {
   const float* src;
   int64_t s_row, s_k;
   int rows;
-  __nv_bfloat16* dst;
-  uint32_t slots;  // 2 bits per slot of a segment: which term (0 h, 1 m, 2 l) it takes
+  __nv_bfloat16* dst;  // [3 terms][rows][ld]
 };
 
-constexpr int SPLIT_SEGMENT = 256;                    // original k per accumulator: 96 bf16 instructions
+constexpr int SPLIT_SEGMENT = 256;                    // k per accumulator: 4 k-blocks x 6 products x 4 instructions
 constexpr int64_t SPLIT_MIN_WORK = 1ll << 21;         // below this the CUDA-core kernel's single launch wins
 constexpr size_t SPLIT_MAX_SCRATCH = 3ull << 30;      // split copies larger than this stay on the CUDA cores
-constexpr uint32_t SLOTS_A = 0u | (0u << 2) | (1u << 4) | (1u << 6) | (0u << 8) | (2u << 10);
-constexpr uint32_t SLOTS_B = 0u | (1u << 2) | (0u << 4) | (1u << 6) | (2u << 8) | (0u << 10);
 
 // Both operands in one launch: blockIdx.z selects A or B. A block handles 32 rows x 64 k
 // through shared memory, so that the read (along whichever of row / k is contiguous in src) is
-// coalesced; each thread then splits 8 consecutive k of one row and writes six 16-byte vectors.
+// coalesced; each thread then splits 8 consecutive k of one row and writes three 16-byte vectors.
 __global__ void __launch_bounds__(256) split_bf16x3_kernel(const SplitOperand oa, const SplitOperand ob, int K, int64_t ld) {
   __shared__ float tile[32][65];
   const SplitOperand& o = blockIdx.z == 0 ? oa : ob;
@@ -735,7 +772,7 @@ __global__ void __launch_bounds__(256) split_bf16x3_kernel(const SplitOperand oa
   __nv_bfloat16 term[3][8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
-    const float x = tile[i][g * 8 + e];
+    const float x = tile[i][g * 8 + e];  // zero beyond K
     const __nv_bfloat16 h = __float2bfloat16_rn(x);
     const float x1 = x - __bfloat162float(h);
     const __nv_bfloat16 m = __float2bfloat16_rn(x1);
@@ -744,24 +781,15 @@ __global__ void __launch_bounds__(256) split_bf16x3_kernel(const SplitOperand oa
     term[1][e] = m;
     term[2][e] = __float2bfloat16_rn(x2);
   }
-  // k belongs to segment k / SPLIT_SEGMENT, which owns columns [6 * first, 6 * (first + len))
-  // as six slots of len; a group of 8 never straddles a segment (segments are multiples of 8)
-  const int first = (k / SPLIT_SEGMENT) * SPLIT_SEGMENT;
-  const int len = min(SPLIT_SEGMENT, K - first);
-  __nv_bfloat16* out = o.dst + r * ld + 6 * static_cast<int64_t>(first) + (k - first);
-  if ((len & 7) == 0) {
+  // rows are `ld` (a multiple of 8) long, so the whole group of 8 is inside the row
+  __nv_bfloat16* out = o.dst + r * ld + k;
+  const int64_t term_stride = static_cast<int64_t>(o.rows) * ld;
 #pragma unroll
-    for (int sl = 0; sl < 6; ++sl)
-      *reinterpret_cast<uint4*>(out + sl * len) = *reinterpret_cast<const uint4*>(term[(o.slots >> (2 * sl)) & 3u]);
-  } else {
-    // a ragged last segment: its slots do not start on 16-byte boundaries
-    const int n = min(8, K - k);
-    for (int sl = 0; sl < 6; ++sl)
-      for (int e = 0; e < n; ++e) out[sl * len + e] = term[(o.slots >> (2 * sl)) & 3u][e];
-  }
+  for (int t = 0; t < 3; ++t) *reinterpret_cast<uint4*>(out + t * term_stride) = *reinterpret_cast<const uint4*>(term[t]);
 }
 
-inline int64_t split_ld(int K) { return (6ll * K + 7) & ~7ll; }  // rows 16-byte aligned
+inline int64_t split_ld(int K) { return (static_cast<int64_t>(K) + 7) & ~7ll; }  // rows 16-byte aligned
+inline size_t split_operand_bytes(int rows, int K) { return (static_cast<size_t>(rows) * split_ld(K) * 2 * 3 + 255) & ~static_cast<size_t>(255); }
 
 }  // namespace
 
@@ -772,8 +800,7 @@ int gemm_tc_split_f32_supported(const lh_ctx* ctx, const GemmProblem& p) {
   if (p.a_dtype != LH_F32 || p.b_dtype != LH_F32 || p.d_dtype != LH_F32) return 0;
   if (p.M < 1 || p.K < 1 || p.N < 8 || p.N % 8) return 0;
   if (static_cast<int64_t>(p.M) * p.N * p.K < SPLIT_MIN_WORK) return 0;
-  const size_t scratch = static_cast<size_t>(split_ld(p.K)) * 2 * (static_cast<size_t>(p.M) + p.N);
-  if (scratch > SPLIT_MAX_SCRATCH) return 0;
+  if (split_operand_bytes(p.M, p.K) + split_operand_bytes(p.N, p.K) > SPLIT_MAX_SCRATCH) return 0;
   auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
   if (p.sdn != 1 || (p.sdm % 4) != 0 || p.sdm < p.N || !aligned16(p.D)) return 0;
   if (p.C && (p.c_dtype != LH_F32 || p.scn != 1 || (p.scm % 4) != 0 || !aligned16(p.C))) return 0;
@@ -784,22 +811,20 @@ int gemm_tc_split_f32_supported(const lh_ctx* ctx, const GemmProblem& p) {
 
 size_t gemm_tc_split_f32_scratch_bytes(int M, int N, int K) {
   if (M < 1 || K < 1 || N < 8 || N % 8 || static_cast<int64_t>(M) * N * K < SPLIT_MIN_WORK) return 0;
-  const size_t a_bytes = static_cast<size_t>(M) * split_ld(K) * 2, b_bytes = static_cast<size_t>(N) * split_ld(K) * 2;
-  const size_t total = ((a_bytes + 255) & ~static_cast<size_t>(255)) + b_bytes;
+  const size_t total = split_operand_bytes(M, K) + split_operand_bytes(N, K);
   return total > SPLIT_MAX_SCRATCH ? 0 : total;
 }
 
 int gemm_tc_split_f32_launch(lh_ctx* ctx, const GemmProblem& p) {
   const int64_t ld = split_ld(p.K);
-  const size_t a_bytes = static_cast<size_t>(p.M) * ld * 2, b_bytes = static_cast<size_t>(p.N) * ld * 2;
-  const size_t a_pad = (a_bytes + 255) & ~static_cast<size_t>(255);
-  int rc = ensure_scratch(ctx, a_pad + b_bytes);
+  const size_t a_bytes = split_operand_bytes(p.M, p.K), b_bytes = split_operand_bytes(p.N, p.K);
+  int rc = ensure_scratch(ctx, a_bytes + b_bytes);
   if (rc) return rc;
-  __nv_bfloat16* a6 = static_cast<__nv_bfloat16*>(ctx->scratch);
-  __nv_bfloat16* b6 = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ctx->scratch) + a_pad);
+  __nv_bfloat16* a3 = static_cast<__nv_bfloat16*>(ctx->scratch);
+  __nv_bfloat16* b3 = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ctx->scratch) + a_bytes);
   {
-    const SplitOperand oa{static_cast<const float*>(p.A), p.sam, p.sak, p.M, a6, SLOTS_A};
-    const SplitOperand ob{static_cast<const float*>(p.B), p.sbn, p.sbk, p.N, b6, SLOTS_B};
+    const SplitOperand oa{static_cast<const float*>(p.A), p.sam, p.sak, p.M, a3};
+    const SplitOperand ob{static_cast<const float*>(p.B), p.sbn, p.sbk, p.N, b3};
     const int max_rows = p.M > p.N ? p.M : p.N;
     const dim3 grid((p.K + 63) / 64, (max_rows + 31) / 32, 2);
     split_bf16x3_kernel<<<grid, 256, 0, ctx->stream>>>(oa, ob, p.K, ld);
@@ -807,19 +832,15 @@ int gemm_tc_split_f32_launch(lh_ctx* ctx, const GemmProblem& p) {
   }
   const int sms = ctx->sm_count - ctx->reserved_sms > 0 ? ctx->sm_count - ctx->reserved_sms : 1;
   const int64_t num_m = (p.M + BM - 1) / BM;
-  const int64_t tiles256 = num_m * ((p.N + 255) / 256), tiles128 = num_m * ((p.N + 127) / 128);
+  const int64_t tiles128 = num_m * ((p.N + 127) / 128);
   const int nseg = (p.K + SPLIT_SEGMENT - 1) / SPLIT_SEGMENT;
-  // Small and medium products: 64- or 128-wide tiles (whichever still gives every SM a tile)
-  // with four segment accumulators each, so a whole k range of 1024 is ONE launch (launch
-  // latency is what such products cost). Large ones: the wider tile's efficiency matters more
-  // than the launch count: two segments per launch.
-  // The caller's tile hint (bits 8-15 of the flags) overrides the choice below.
+  // 128-wide tiles (two three-term stages of 96 KB) once they fill the GPU, 64-wide ones (two
+  // stages of 72 KB, twice the CTAs) below that; four segment accumulators per tile either way,
+  // so a k range of 1024 is ONE GEMM launch. The caller's tile hint (bits 8-15 of the flags)
+  // overrides the choice.
   const int hint = static_cast<int>((p.flags >> 8) & 0xffu) * 8;
-  const int bn = (hint == 64 || hint == 128 || hint == 256) ? hint
-                 : tiles256 >= 2 * static_cast<int64_t>(sms) ? 256
-                 : tiles128 >= sms ? 128 : 64;
-  const bool wide = bn == 256;
-  const int per_launch = wide ? 2 : 4;
+  const int bn = (hint == 64 || hint == 128) ? hint : tiles128 >= sms ? 128 : 64;
+  const int per_launch = 4;
   for (int s0 = 0; s0 < nseg; s0 += per_launch) {
     const int s1 = s0 + per_launch < nseg ? s0 + per_launch : nseg;
     const int first = s0 * SPLIT_SEGMENT;
@@ -827,9 +848,9 @@ int gemm_tc_split_f32_launch(lh_ctx* ctx, const GemmProblem& p) {
     const bool is_first = s0 == 0, is_last = s1 == nseg;
     GemmProblem q = p;
     q.a_dtype = LH_BF16; q.b_dtype = LH_BF16;
-    q.K = 6 * (last_k - first);
-    q.A = a6 + 6 * static_cast<int64_t>(first); q.sam = ld; q.sak = 1;
-    q.B = b6 + 6 * static_cast<int64_t>(first); q.sbn = ld; q.sbk = 1;
+    q.K = last_k - first;
+    q.A = a3 + first; q.sam = ld; q.sak = 1;
+    q.B = b3 + first; q.sbn = ld; q.sbk = 1;
     EpiParams epi;
     epi.D = p.D; epi.d_dtype = p.d_dtype; epi.ldd = p.sdm;
     // the caller's C enters with the first launch, the running sum (D) with the later ones;
@@ -840,10 +861,10 @@ int gemm_tc_split_f32_launch(lh_ctx* ctx, const GemmProblem& p) {
     epi.act = is_last ? p.act : LH_ACT_NONE;
     epi.swiglu = 0;
     epi.rope_table = nullptr; epi.rope_cols = 0; epi.rope_dim = 0; epi.rope_seq = 0;
-    const int seg_k_blocks = 6 * SPLIT_SEGMENT / BK;  // a full segment is 1536 bf16 columns = 24 k-blocks of 64
-    rc = wide        ? launch_variant<256, true, 4, true, 2>(ctx, q, epi, seg_k_blocks)
-         : bn == 128 ? launch_variant<128, true, 6, true, 4>(ctx, q, epi, seg_k_blocks)
-                     : launch_variant<64, true, 8, true, 4>(ctx, q, epi, seg_k_blocks);
+    const int seg_k_blocks = SPLIT_SEGMENT / BK;
+    const int64_t ts_a = static_cast<int64_t>(p.M) * ld, ts_b = static_cast<int64_t>(p.N) * ld;
+    rc = bn == 128 ? launch_variant<128, true, 2, true, 4, 3>(ctx, q, epi, seg_k_blocks, ts_a, ts_b)
+                   : launch_variant<64, true, 2, true, 4, 3>(ctx, q, epi, seg_k_blocks, ts_a, ts_b);
     if (rc) return rc;
   }
   return LH_OK;
