@@ -425,7 +425,7 @@ def run_decoder(args, dist: Dist, which: str) -> dict:
 # `ncu --clock-control none -k regex:<kernel> -c 2..8` on this file's own workloads (the GEMM
 # and attention workloads as they are; the decoder's GEMM launches on a 2-layer stack, summed
 # per layer and multiplied by the layer count, traffic being the same for every layer).
-NCU_TRAFFIC_BYTES = {"gemm_4096": 92.8e6, "attention_full": 250.8e6}
+NCU_TRAFFIC_BYTES = {"gemm_4096": 83.7e6, "attention_full": 244.8e6, "attention_causal": 561.4e6, "llama_gemms_per_layer": 5.158e9}
 # The f32 GEMM runs as six bf16 products per f32 product (each operand split into three bf16
 # terms): its ceiling is a sixth of the measured bf16 peak.
 F32_VIA_SIX_BF16_FRACTION_OF_BF16 = 1.0 / 6.0
@@ -552,8 +552,8 @@ def kernel_attention(ctx, peaks, source, causal=False, steps=20, warmup=5) -> di
     achieved = flops / mean_s / 1e12
     return {
         "ms": round(mean_s * 1e3, 5), "tflops": round(achieved, 1), "causal": causal, "shape": [B, H, S, Dh],
-        "roofline": {"bound": "tensor", "kernel": "attn_fwd_tc2_kernel", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{source} cuBLAS bf16, burst (kernel timed alone)", "traffic": None if causal else NCU_TRAFFIC_BYTES["attention_full"]},
+        "roofline": {"bound": "tensor", "kernel": "attn_fwd_tc3_kernel", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{source} cuBLAS bf16, burst (kernel timed alone)", "traffic": NCU_TRAFFIC_BYTES["attention_causal" if causal else "attention_full"]},
         "host": (q, k, v, o),
     }
 
