@@ -235,6 +235,12 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched only this CTA's shared and tensor memory, so it may run while the
+  // kernel before this one in the stream drains (the launch below asks for that). Every CTA of
+  // this persistent grid is resident by now: the next kernel may take SMs as they fall free.
+  // From here on global memory is read, by every role: all threads wait for the predecessor.
+  grid_dependency_trigger();
+  grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -619,7 +625,20 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int
   const bool split_tail = BN == 256 && SEGS == 1 && !epi.swiglu && leftover > 0 && 2 * leftover <= grid;
   p.first_half_item = split_tail ? num_tiles - leftover : num_tiles;
   p.num_items = split_tail ? num_tiles + leftover : num_tiles;
-  kernel<<<grid, NUM_THREADS, L::DYN_BYTES, ctx->stream>>>(tmA, tmB, tmD, p);
+  // Programmatic dependent launch: this kernel's CTAs may start (barrier set-up, tensor-memory
+  // allocation) on SMs the previous kernel in the stream has already left; they wait for its
+  // completion before their first global access (grid_dependency_wait in the kernel).
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = L::DYN_BYTES;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  LH_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmD, p));
   LH_CHECK_LAUNCH(ctx, "gemm_bf16_tc_kernel");
   return LH_OK;
 }

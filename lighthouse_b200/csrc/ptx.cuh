@@ -39,6 +39,15 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+// Programmatic dependent launch. `grid_dependency_wait`: until the kernels before this one in
+// the stream have completed and their writes are visible (a no-op for a kernel launched the
+// plain way). `grid_dependency_trigger`: once every CTA of this kernel has executed it (or
+// exited), a dependent kernel launched with the programmatic attribute may start its CTAs on
+// whatever SM resources have become free; that kernel still waits, by the call above, for this
+// one to complete before it reads anything.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(
