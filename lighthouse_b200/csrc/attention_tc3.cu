@@ -208,6 +208,12 @@ attn_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Set-up above touched only this CTA's shared and tensor memory and may run while the kernel
+  // before this one drains (programmatic dependent launch, see the launch); every CTA of this
+  // persistent grid is resident, so the next kernel may take SMs as they fall free. Global
+  // memory is read from here on: all threads wait for the predecessor first.
+  grid_dependency_trigger();
+  grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -730,7 +736,17 @@ int launch3_hd(lh_ctx* ctx, const AttnProblem& a) {
   auto kernel = attn_fwd_tc3_kernel<HD>;
   LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   const int grid = items < usable_sms(ctx) ? static_cast<int>(items) : usable_sms(ctx);  // one persistent CTA per SM
-  kernel<<<static_cast<unsigned>(grid), ATT3_THREADS, L::DYN_BYTES, ctx->stream>>>(tmQ, tmK, tmV, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(ATT3_THREADS);
+  cfg.dynamicSmemBytes = L::DYN_BYTES;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // CTAs may set up while the previous kernel drains
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  LH_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, kernel, tmQ, tmK, tmV, p));
   LH_CHECK_LAUNCH(ctx, "attn_fwd_tc3_kernel");
   return LH_OK;
 }

@@ -6,6 +6,7 @@
 // only to combine warps; rows longer than 8192 elements or not vectorisable fall back to
 // a block-per-row kernel that re-reads the row from L2.
 #include "common.cuh"
+#include "ptx.cuh"
 #include "epilogue.cuh"
 
 namespace lh {
@@ -49,6 +50,9 @@ struct RowParams {
 // its type switch, and the kernel is bound by instruction issue and fetch instead of HBM.
 template <int VPL, int TPR, int SD = 0>
 __global__ void __launch_bounds__(256, 4) row_group_kernel(const RowParams p) {
+  // a kernel launched as a programmatic dependent may set its CTAs up under this kernel's last
+  // wave of blocks (it still waits for this kernel's completion before it reads anything)
+  grid_dependency_trigger();
   const int x_dtype = SD == 1 ? LH_BF16 : SD == 2 ? LH_F32 : p.x_dtype;
   const int out_dtype = SD != 0 ? LH_BF16 : p.out_dtype;
   const int gamma_dtype = SD == 1 ? LH_BF16 : SD == 2 ? LH_F32 : p.gamma_dtype;
@@ -392,6 +396,9 @@ __device__ __forceinline__ float ew_apply(int kind, int act, float scalar, float
 
 // All operands contiguous (b optionally a last-dim vector): 8 elements per thread.
 __global__ void __launch_bounds__(256) ew_vec_kernel(const EwParams p) {
+  // a kernel launched as a programmatic dependent may set its CTAs up under this kernel's last
+  // wave of blocks (it still waits for this kernel's completion before it reads anything)
+  grid_dependency_trigger();
   const int64_t nvec = p.total / 8;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
