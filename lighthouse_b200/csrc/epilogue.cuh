@@ -55,8 +55,10 @@ __device__ __forceinline__ float apply_act(float x, int act) {
       const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
       return __fdividef(x, 1.f + __expf(-2.f * u));
     }
-    case LH_ACT_SILU: return x / (1.f + __expf(-x));
-    case LH_ACT_SIGMOID: return 1.f / (1.f + __expf(-x));
+    // (fast division: two special-function instructions and a multiply; the IEEE divide is a
+    // dozen instructions with a slow path, which made an epilogue three times its main loop)
+    case LH_ACT_SILU: return __fdividef(x, 1.f + __expf(-x));
+    case LH_ACT_SIGMOID: return __fdividef(1.f, 1.f + __expf(-x));
     default: return x;
   }
 }
