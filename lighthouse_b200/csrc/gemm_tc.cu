@@ -458,7 +458,12 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tmem_ld_32x32b_x32(taddr + BN / 2 + u * CHUNK + h * 32, u_);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[h * 32 + i] = apply_act(__uint_as_float(g_[i]), LH_ACT_SILU) * __uint_as_float(u_[i]);
+            for (int i = 0; i < 32; ++i) {
+              // IEEE divide here (this epilogue hides under a main loop over K >= 4096 and the
+              // product feeds a contraction over 14336 terms)
+              const float gv = __uint_as_float(g_[i]);
+              v[h * 32 + i] = gv / (1.f + __expf(-gv)) * __uint_as_float(u_[i]);
+            }
           }
         }
         if (u == units - 1) {
