@@ -468,15 +468,24 @@ def build_llama_plan_overlapped(cfg: LlamaConfig, rank: int, tp: int, microbatch
         p.rmsnorm(mine, h[mb], weight, cfg.eps)
         p.allgather(full, mine)
 
-    # Nothing runs beside the first micro-batch's first chain and the last one's last chain:
-    # they get the whole GPU; in between the GEMMs leave ``reserve_sms`` SMs to the side stream.
+    # Nothing runs beside the last micro-batch's last chain: it gets the whole GPU; before that
+    # the GEMMs leave ``reserve_sms`` SMs to the side stream.
+    # The input is replicated, so the first micro-batch's first norm needs no exchange: every rank
+    # normalises all of its rows itself, on the main stream, which has nothing else to do yet
+    # (a norm-and-gather there made the first GEMM wait for the slowest rank to arrive: 0.15 ms
+    # at 8 GPUs). The other micro-batches' first chains run beside the first one's GEMMs.
     for mb in range(m):
+        if mb == 0:
+            p.elementwise("copy", h[0], p.arg(1).slice(0, rank * ts, ts))
+            p.rmsnorm(xn[0], p.arg(1).slice(0, 0, tm), layer_args(0)["attention_norm"], cfg.eps)
+            chain.ready[0] = chain.event()
+            p.event_record(chain.ready[0])
+            p.reserve_sms(reserve_sms)
+            continue
         chain.fork()
         p.elementwise("copy", h[mb], p.arg(1).slice(0, mb * tm + rank * ts, ts))
         norm_and_gather(mb, layer_args(0)["attention_norm"], False, reduce=False)
         chain.join(mb)
-        if mb == 0:
-            p.reserve_sms(reserve_sms)
     to_bhsd = lambda z: z.permute((0, 2, 1, 3))
     for li in range(cfg.n_layer):
         a = layer_args(li)

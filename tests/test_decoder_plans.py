@@ -181,7 +181,9 @@ def test_overlapped_schedule_is_the_same_computation_and_is_fully_ordered():
     plan = D.build_llama_plan_overlapped(LLAMA, 0, 1, microbatches=2)
     kinds = plan.kinds()
     n_sub = 2 * LLAMA.n_layer * 2
-    assert kinds.count("reducescatter") == n_sub and kinds.count("allgather") == n_sub + 2
+    # one gather per contraction, plus the first norm of every micro-batch but the first (whose
+    # rows each rank normalises itself: the input is replicated)
+    assert kinds.count("reducescatter") == n_sub and kinds.count("allgather") == n_sub + 1
     assert kinds.count("reserve_sms") == 2 and plan.ops[[i for i, k in enumerate(kinds) if k == "reserve_sms"][-1]].attrs["index"] == 0
     # drop the main stream's wait for the first gathered activations: a read-before-write race
     waits = [i for i, op in enumerate(plan.ops) if op.kind == "event_wait" and i + 1 < len(plan.ops) and plan.ops[i + 1].kind == "gemm"]
@@ -194,13 +196,13 @@ def test_overlapped_schedule_is_the_same_computation_and_is_fully_ordered():
         D.build_llama_plan_overlapped(LLAMA, 0, 1, microbatches=3)
     # the fused form: same schedule, one operator per side chain, symmetric buffers as arguments
     fused = D.build_llama_plan_overlapped(LLAMA, 0, 1, microbatches=2, fused=True)
-    assert fused.kinds().count("reduce_norm_gather") == n_sub + 2 and "reducescatter" not in fused.kinds()
+    assert fused.kinds().count("reduce_norm_gather") == n_sub + 1 and "reducescatter" not in fused.kinds()
     assert len(fused.args) == len(plan.args) + 4 and fused.args[-1].name == "xn1"
     got = run_llama_rank(LLAMA, w, x, 0, 1, overlapped=True, fused=True)
     assert max_rel_err(got, plain) < 2e-2
     # with a symmetric result buffer the last layer gathers straight into it: no copy, same values
     direct = D.build_llama_plan_overlapped(LLAMA, 0, 1, microbatches=2, fused=True, result_symmetric=True)
-    assert direct.kinds().count("reduce_norm_gather") == n_sub + 2 and direct.kinds().count("ew:copy") == fused.kinds().count("ew:copy") - 2
+    assert direct.kinds().count("reduce_norm_gather") == n_sub + 1 and direct.kinds().count("ew:copy") == fused.kinds().count("ew:copy") - 2
     assert np.array_equal(run_llama_rank(LLAMA, w, x, 0, 1, overlapped=True, fused=True, result_symmetric=True), got)
 
 
