@@ -150,12 +150,12 @@ __device__ __forceinline__ void activate_block(float (&v)[N_], int act) {
   }
 }
 
-// Adds the 128 bytes of a C / residual row segment held in eight 16-byte registers.
+// Adds a row segment of N_ values held in 16-byte registers (4 f32 or 8 bf16 each).
 template <bool F32, int N_>
 __device__ __forceinline__ void add_row_segment(float (&v)[N_], const uint4 (&seg)[8]) {
   if (F32) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < N_ / 4; ++j) {
       v[j * 4 + 0] += __uint_as_float(seg[j].x);
       v[j * 4 + 1] += __uint_as_float(seg[j].y);
       v[j * 4 + 2] += __uint_as_float(seg[j].z);
@@ -163,7 +163,7 @@ __device__ __forceinline__ void add_row_segment(float (&v)[N_], const uint4 (&se
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < N_ / 8; ++j) {
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&seg[j]);
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
@@ -175,14 +175,15 @@ __device__ __forceinline__ void add_row_segment(float (&v)[N_], const uint4 (&se
   }
 }
 
-// Loads this lane's 128-byte row segment (8 x 16 bytes) starting at element `elem0`;
-// vectors past column `n_out` are skipped (n_out is a multiple of 8).
-template <bool F32>
+// Loads this lane's row segment of N_ values (16-byte vectors of 4 f32 or 8 bf16) starting at
+// element `elem0`; vectors past column `n_out` are skipped (n_out is a multiple of 8).
+template <bool F32, int N_>
 __device__ __forceinline__ void load_row_segment(uint4 (&seg)[8], const void* base, int64_t elem0, int col0, int n_out) {
   constexpr int EPV = F32 ? 4 : 8;
+  constexpr int NV = N_ / EPV;
   const char* ptr = static_cast<const char*>(base) + elem0 * (F32 ? 4 : 2);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < NV; ++j) {
     seg[j] = (col0 + j * EPV < n_out) ? __ldg(reinterpret_cast<const uint4*>(ptr) + j) : make_uint4(0u, 0u, 0u, 0u);
   }
 }
@@ -191,7 +192,9 @@ __device__ __forceinline__ void load_row_segment(uint4 (&seg)[8], const void* ba
 // in its own accumulator (SEGS * BN columns of tensor memory, no double buffering across tiles)
 // and the segments' sums are added with correctly rounded f32 adds in the epilogue: the tensor
 // core adds into an accumulator with truncation, which biases long sums.
-template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, int SEGS = 1, int TERMS = 1>
+// EPI32: bf16 results in units of 32 columns instead of 64 (launch_variant picks it when the
+// epilogue applies an activation with special-function work).
+template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, int SEGS = 1, int TERMS = 1, bool EPI32 = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmD, const GemmTcParams p) {
@@ -388,8 +391,14 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int row = row0 + lane;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      // Output columns of this tile, one 128-byte row segment (CHUNK columns) at a time.
-      constexpr int CHUNK = OUT_F32 ? 32 : 64;
+      // Output columns of this tile, CHUNK at a time. bf16 results normally go 64 at a time (one
+      // stored block per unit: the least per-unit overhead). With an activation that has
+      // special-function work, units of 64 left an epilogue warp, alone on its scheduler, with a
+      // dependent chain per element that the compiler, at its register limit, did not interleave
+      // (erf-GELU on bf16 results 150 us where f32 results, 32 wide, took 112): those launches use
+      // units of 32, two per stored block (121 us; without an activation 32-wide units cost 10 %).
+      constexpr int CHUNK = (OUT_F32 || EPI32) ? 32 : 64;  // columns per unit of work
+      constexpr int PER_STORE = OUT_F32 ? 1 : 64 / CHUNK;  // units per stored block (a 128-byte row segment)
       const int out_cols = (e.swiglu || w.is_half) ? BN / 2 : BN;
       const int out_col_base = e.swiglu ? n_blk * (BN / 2) : n_blk * BN + w.half * (BN / 2);
       const int units = out_cols / CHUNK;
@@ -415,6 +424,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           bq[4] = b1.x; bq[5] = b1.y; bq[6] = b1.z; bq[7] = b1.w;
         }
       }
+      bool pending = false;  // bf16 results: the first half of a 64-column store block is staged
 #pragma unroll 1
       for (int u = 0; u < units; ++u) {
         const int col0 = out_col_base + u * CHUNK;
@@ -426,24 +436,17 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!e.swiglu) {
           uint32_t raw[CHUNK];
 #pragma unroll
-          for (int h = 0; h < CHUNK / 32; ++h) {
-            uint32_t(&part)[32] = *reinterpret_cast<uint32_t(*)[32]>(&raw[h * 32]);
-            tmem_ld_32x32b_x32(taddr + u * CHUNK + h * 32, part);
-          }
+          for (int h = 0; h < CHUNK / 32; ++h) tmem_ld_32x32b_x32(taddr + u * CHUNK + h * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[h * 32]));
           // C / residual rows travel while the tensor-memory load is in flight
-          if (use_c) load_row_segment<OUT_F32>(cseg, e.C, row_ok ? static_cast<int64_t>(row) * e.ldc + col0 : 0, row_ok ? col0 : p.n_out, p.n_out);
-          if (use_r) load_row_segment<OUT_F32>(rseg, e.R, row_ok ? static_cast<int64_t>(row) * e.ldr + col0 : 0, row_ok ? col0 : p.n_out, p.n_out);
+          if (use_c) load_row_segment<OUT_F32, CHUNK>(cseg, e.C, row_ok ? static_cast<int64_t>(row) * e.ldc + col0 : 0, row_ok ? col0 : p.n_out, p.n_out);
+          if (use_r) load_row_segment<OUT_F32, CHUNK>(rseg, e.R, row_ok ? static_cast<int64_t>(row) * e.ldr + col0 : 0, row_ok ? col0 : p.n_out, p.n_out);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < CHUNK; ++i) v[i] = __uint_as_float(raw[i]);
           if (SEGS > 1) {
             // the later segments' sums, added one by one with rounded f32 adds
             for (int sg = 1; sg < nseg; ++sg) {
-#pragma unroll
-              for (int h = 0; h < CHUNK / 32; ++h) {
-                uint32_t(&part)[32] = *reinterpret_cast<uint32_t(*)[32]>(&raw[h * 32]);
-                tmem_ld_32x32b_x32(taddr + sg * BN + u * CHUNK + h * 32, part);
-              }
+              tmem_ld_32x32b_x32(taddr + sg * BN + u * CHUNK, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));  // f32 results: CHUNK = 32
               tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < CHUNK; ++i) v[i] += __uint_as_float(raw[i]);
@@ -471,67 +474,78 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tc_fence_before_sync();
           mbar_arrive(&tmem_empty[buf]);
         }
-        if (!active) continue;
-        if (!e.swiglu) {
-          if (use_c) add_row_segment<OUT_F32>(v, cseg);
-          if (e.bias) {
-            // lane (u * CHUNK) / 8 + g holds the bias of this unit's g-th group of 8 columns
-#pragma unroll
-            for (int g = 0; g < CHUNK / 8; ++g) {
-              const int src = u * (CHUNK / 8) + g;
-#pragma unroll
-              for (int i = 0; i < 8; ++i) v[g * 8 + i] += __shfl_sync(0xffffffffu, bq[i], src);
-            }
-          }
-          // 32 values at a time: on 64 at once the compiler, at its register limit, serialised the
-          // erf polynomial (bf16 results: 180 us against 112 us for f32 results, whose units are 32 wide)
-#pragma unroll
-          for (int h = 0; h < CHUNK / 32; ++h) activate_block(*reinterpret_cast<float(*)[32]>(&v[h * 32]), e.act);
-          if (use_r) add_row_segment<OUT_F32>(v, rseg);
-          if (!OUT_F32 && col0 < e.rope_cols) {
-            // Rotary embedding on the way out: pairs (2i, 2i+1) of a head are neighbours in
-            // this thread's registers. The value is first rounded to the output type, as a
-            // separate rotary kernel reading the stored projection would see it.
-            const int pos = row_ok ? row % e.rope_seq : 0;
-            const float4* tab = reinterpret_cast<const float4*>(e.rope_table) +
-                                (static_cast<int64_t>(pos) * (e.rope_dim / 2) + (col0 % e.rope_dim) / 2) / 2;
-#pragma unroll
-            for (int j = 0; j < CHUNK / 4; ++j) {
-              const float4 cs = __ldg(tab + j);  // (cos, sin) of two pairs
-              const float x0 = __bfloat162float(__float2bfloat16_rn(v[4 * j])), x1 = __bfloat162float(__float2bfloat16_rn(v[4 * j + 1]));
-              const float x2 = __bfloat162float(__float2bfloat16_rn(v[4 * j + 2])), x3 = __bfloat162float(__float2bfloat16_rn(v[4 * j + 3]));
-              v[4 * j] = x0 * cs.x - x1 * cs.y;
-              v[4 * j + 1] = x0 * cs.y + x1 * cs.x;
-              v[4 * j + 2] = x2 * cs.z - x3 * cs.w;
-              v[4 * j + 3] = x2 * cs.w + x3 * cs.z;
-            }
-          }
-        }
+        // bf16 results leave in blocks of 64 columns (one 128-byte row segment): two units
+        // share a staging buffer and a store
+        const int part = u % PER_STORE;
         uint8_t* sb = stage_bufs + sbuf * STAGING_BUF_BYTES;
-        if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer is done
-        __syncwarp();
-        if (!OUT_F32) {
+        if (active) {
+          if (!e.swiglu) {
+            if (use_c) add_row_segment<OUT_F32>(v, cseg);
+            if (e.bias) {
+              // lane (u * CHUNK) / 8 + g holds the bias of this unit's g-th group of 8 columns
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            uint4 q;
-            q.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
-            q.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
-            q.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
-            q.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
-            stage_chunk(sb, lane, j, q);
+              for (int g = 0; g < CHUNK / 8; ++g) {
+                const int src = u * (CHUNK / 8) + g;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[g * 8 + i] += __shfl_sync(0xffffffffu, bq[i], src);
+              }
+            }
+#pragma unroll
+            for (int h = 0; h < CHUNK / 32; ++h) activate_block(*reinterpret_cast<float(*)[32]>(&v[h * 32]), e.act);
+            if (use_r) add_row_segment<OUT_F32>(v, rseg);
+            if (!OUT_F32 && col0 < e.rope_cols) {
+              // Rotary embedding on the way out: pairs (2i, 2i+1) of a head are neighbours in
+              // this thread's registers. The value is first rounded to the output type, as a
+              // separate rotary kernel reading the stored projection would see it.
+              const int pos = row_ok ? row % e.rope_seq : 0;
+              const float4* tab = reinterpret_cast<const float4*>(e.rope_table) +
+                                  (static_cast<int64_t>(pos) * (e.rope_dim / 2) + (col0 % e.rope_dim) / 2) / 2;
+#pragma unroll
+              for (int j = 0; j < CHUNK / 4; ++j) {
+                const float4 cs = __ldg(tab + j);  // (cos, sin) of two pairs
+                const float x0 = __bfloat162float(__float2bfloat16_rn(v[4 * j])), x1 = __bfloat162float(__float2bfloat16_rn(v[4 * j + 1]));
+                const float x2 = __bfloat162float(__float2bfloat16_rn(v[4 * j + 2])), x3 = __bfloat162float(__float2bfloat16_rn(v[4 * j + 3]));
+                v[4 * j] = x0 * cs.x - x1 * cs.y;
+                v[4 * j + 1] = x0 * cs.y + x1 * cs.x;
+                v[4 * j + 2] = x2 * cs.z - x3 * cs.w;
+                v[4 * j + 3] = x2 * cs.w + x3 * cs.z;
+              }
+            }
           }
-        } else {
+          if (part == 0) {
+            if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer is done
+            __syncwarp();
+          }
+          if (!OUT_F32) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            stage_chunk(sb, lane, j, make_uint4(__float_as_uint(v[j * 4]), __float_as_uint(v[j * 4 + 1]), __float_as_uint(v[j * 4 + 2]), __float_as_uint(v[j * 4 + 3])));
+            for (int j = 0; j < CHUNK / 8; ++j) {
+              uint4 q;
+              q.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+              q.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+              q.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+              q.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+              stage_chunk(sb, lane, part * (CHUNK / 8) + j, q);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              stage_chunk(sb, lane, j, make_uint4(__float_as_uint(v[j * 4]), __float_as_uint(v[j * 4 + 1]), __float_as_uint(v[j * 4 + 2]), __float_as_uint(v[j * 4 + 3])));
+          }
+          pending = true;
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_2d(&tmD, sb, col0, row0);
-          bulk_commit_group();
+        // the block goes out after its last unit (columns past the edge of D are clipped by
+        // the store, so a first half alone is complete)
+        const bool last_of_block = part == PER_STORE - 1 || u == units - 1;
+        if (pending && last_of_block) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmD, sb, col0 - part * CHUNK, row0);
+            bulk_commit_group();
+          }
+          sbuf ^= 1;
+          pending = false;
         }
-        sbuf ^= 1;
       }
     }
     if (lane == 0) bulk_wait_group<0>();  // all stores of this warp have landed
@@ -554,7 +568,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 // TERMS = 3: pr.A / pr.B point at three consecutive (rows, ld) bf16 arrays, the terms of the f32
 // operands, `term_stride_a` / `term_stride_b` elements apart; pr.K is the f32 operands' k range.
-template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, int SEGS = 1, int TERMS = 1>
+template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, int SEGS = 1, int TERMS = 1, bool EPI32 = false>
 int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int seg_k_blocks = 0, int64_t term_stride_a = 0,
                    int64_t term_stride_b = 0) {
   using L = SmemLayout<BN, STAGES, TERMS>;
@@ -621,7 +635,7 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int
   p.epi = epi;
   p.seg_k_blocks = seg_k_blocks > 0 ? seg_k_blocks : p.num_k_blocks;
   p.dev_status = ctx->dev_status;
-  auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES, OUT_F32, SEGS, TERMS>;
+  auto kernel = gemm_bf16_tc_kernel<BN, B_KMAJOR, STAGES, OUT_F32, SEGS, TERMS, EPI32>;
   LH_CUDA_CHECK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
   // A persistent grid that fills the GPU would make side-stream kernels (collectives) wait for
@@ -653,6 +667,16 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int
 
 template <bool B_KMAJOR, bool OUT_F32>
 int launch_bn(lh_ctx* ctx, const GemmProblem& p, const EpiParams& epi, int bn) {
+  // bf16 results through an activation with special-function work: 32-column epilogue units
+  const bool epi32 = !OUT_F32 && !epi.swiglu && epi.act != LH_ACT_NONE && epi.act != LH_ACT_RELU;
+  if (epi32) {
+    switch (bn) {
+      case 256: return launch_variant<256, B_KMAJOR, 4, OUT_F32, 1, 1, !OUT_F32>(ctx, p, epi);
+      case 192: return launch_variant<192, B_KMAJOR, 4, OUT_F32, 1, 1, !OUT_F32>(ctx, p, epi);
+      case 128: return launch_variant<128, B_KMAJOR, 6, OUT_F32, 1, 1, !OUT_F32>(ctx, p, epi);
+      default: return launch_variant<64, B_KMAJOR, 8, OUT_F32, 1, 1, !OUT_F32>(ctx, p, epi);
+    }
+  }
   switch (bn) {
     case 256: return launch_variant<256, B_KMAJOR, 4, OUT_F32>(ctx, p, epi);
     case 192: return launch_variant<192, B_KMAJOR, 4, OUT_F32>(ctx, p, epi);
