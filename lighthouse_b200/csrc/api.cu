@@ -242,6 +242,10 @@ extern "C" int lh_b200_sync(lh_ctx_t* ctx) {
   if (st != 0) {
     if (st == 106) ctx->symm_broken = true;  // a peer's flag never came: the ranks are out of step until the flags are set up again
     cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream);
+    // an attention launch that gave up may have left its tiles' arrival counters part-way:
+    // back to zero, or the next launch's merge would trigger on the wrong item
+    for (const AttnSplitPlan& pl : ctx->attn_plans)
+      if (pl.counters) cudaMemsetAsync(pl.counters, 0, static_cast<size_t>(pl.n_slots) * 2 * sizeof(int), ctx->stream);
     cudaStreamSynchronize(ctx->stream);
     return set_error(ctx, LH_ERR_DEVICE, "a kernel gave up on a bounded wait (device status %d)", st);
   }
