@@ -168,6 +168,7 @@ _PROTOTYPES = {
     "lh_b200_event_record": (c_int, [c_void_p, c_int]),
     "lh_b200_event_wait": (c_int, [c_void_p, c_int]),
     "lh_b200_reserve_sms": (c_int, [c_void_p, c_int]),
+    "lh_b200_set_launch_overlap": (c_int, [c_void_p, c_int]),
     "lh_b200_allgather": (c_int, [c_void_p, POINTER(MemRef), POINTER(MemRef)]),
     "lh_b200_module_create": (
         c_int,

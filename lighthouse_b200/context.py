@@ -221,6 +221,12 @@ class CudaContext:
     def reserve_sms(self, n: int) -> None:
         N.check(self._lib.lh_b200_reserve_sms(self.handle, int(n)), self.handle, "lh_b200_reserve_sms")
 
+    def set_launch_overlap(self, enabled: bool) -> None:
+        """Tensor-core kernels as programmatic dependents of their predecessor in the stream
+        (their set-up runs under its tail). Off by default: it pays for kernels queued back to
+        back on one stream and costs where other streams' copies and events interleave."""
+        N.check(self._lib.lh_b200_set_launch_overlap(self.handle, 1 if enabled else 0), self.handle, "lh_b200_set_launch_overlap")
+
     # -- symmetric memory and the fused collective ------------------------------------------
     def symm_register(self, local_ptr: int, nbytes: int, multicast_ptr: int, peer_ptrs: list[int]) -> None:
         """Registers one symmetric buffer: this rank's address, its multicast mapping (0: none)

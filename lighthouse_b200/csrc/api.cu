@@ -636,6 +636,12 @@ extern "C" int lh_b200_reserve_sms(lh_ctx_t* ctx, int n) {
   return LH_OK;
 }
 
+extern "C" int lh_b200_set_launch_overlap(lh_ctx_t* ctx, int enabled) {
+  if (!ctx) return LH_ERR_INVALID;
+  ctx->launch_overlap = enabled != 0;
+  return LH_OK;
+}
+
 extern "C" int lh_b200_allgather(lh_ctx_t* ctx, const lh_memref_t* out, const lh_memref_t* in) {
   if (!ctx || !out || !in) return LH_ERR_INVALID;
   if (!is_contiguous(out) || !is_contiguous(in)) return set_error(ctx, LH_ERR_UNSUPPORTED, "allgather: buffers must be contiguous");

@@ -745,7 +745,7 @@ int launch3_hd(lh_ctx* ctx, const AttnProblem& a) {
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // CTAs may set up while the previous kernel drains
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = ctx->launch_overlap ? 1 : 0;  // off: an ordinary launch, the kernel's grid-dependency calls are no-ops
   LH_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, kernel, tmQ, tmK, tmV, p));
   LH_CHECK_LAUNCH(ctx, "attn_fwd_tc3_kernel");
   return LH_OK;

@@ -64,6 +64,7 @@ struct lh_ctx {
   bool side_selected = false;
   std::vector<cudaEvent_t> events;    // indexed by event number, created on first use
   int reserved_sms = 0;               // SMs persistent kernels leave free
+  bool launch_overlap = false;        // tensor-core kernels launched as programmatic dependents (lh_b200_set_launch_overlap)
   // symmetric memory for the fused collectives
   std::vector<SymmRegion> symm;
   uint32_t* symm_pads[LH_MAX_RANKS] = {nullptr};  // every rank's flag pad as mapped here

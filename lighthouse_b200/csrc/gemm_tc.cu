@@ -570,7 +570,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // operands, `term_stride_a` / `term_stride_b` elements apart; pr.K is the f32 operands' k range.
 template <int BN, bool B_KMAJOR, int STAGES, bool OUT_F32, int SEGS = 1, int TERMS = 1, bool EPI32 = false>
 int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int seg_k_blocks = 0, int64_t term_stride_a = 0,
-                   int64_t term_stride_b = 0) {
+                   int64_t term_stride_b = 0, bool follows_own_kernel = false) {
   using L = SmemLayout<BN, STAGES, TERMS>;
   CUtensorMap tmA, tmB, tmD;
   const int n_out = epi.swiglu ? pr.N / 2 : pr.N;
@@ -647,9 +647,10 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int
   const bool split_tail = BN == 256 && SEGS == 1 && !epi.swiglu && leftover > 0 && 2 * leftover <= grid;
   p.first_half_item = split_tail ? num_tiles - leftover : num_tiles;
   p.num_items = split_tail ? num_tiles + leftover : num_tiles;
-  // Programmatic dependent launch: this kernel's CTAs may start (barrier set-up, tensor-memory
-  // allocation) on SMs the previous kernel in the stream has already left; they wait for its
-  // completion before their first global access (grid_dependency_wait in the kernel).
+  // With launch overlap on (lh_b200_set_launch_overlap): programmatic dependent launch. This
+  // kernel's CTAs may start (barrier set-up, tensor-memory allocation) on SMs the previous
+  // kernel in the stream has already left; they wait for its completion before their first
+  // global access (grid_dependency_wait in the kernel).
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
   cfg.blockDim = dim3(NUM_THREADS);
@@ -659,7 +660,7 @@ int launch_variant(lh_ctx* ctx, const GemmProblem& pr, const EpiParams& epi, int
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = (ctx->launch_overlap || follows_own_kernel) ? 1 : 0;  // off: an ordinary launch, the kernel's grid-dependency calls are no-ops
   LH_CUDA_CHECK(ctx, cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmD, p));
   LH_CHECK_LAUNCH(ctx, "gemm_bf16_tc_kernel");
   return LH_OK;
@@ -798,6 +799,7 @@ constexpr size_t SPLIT_MAX_SCRATCH = 3ull << 30;      // split copies larger tha
 // coalesced; each thread then splits 8 consecutive k of one row and writes three 16-byte vectors.
 __global__ void __launch_bounds__(256) split_bf16x3_kernel(const SplitOperand oa, const SplitOperand ob, int K, int64_t ld) {
   __shared__ float tile[32][65];
+  grid_dependency_trigger();  // the GEMM behind this kernel may set its CTAs up under the last wave of blocks
   const SplitOperand& o = blockIdx.z == 0 ? oa : ob;
   const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 64;
   if (r0 >= o.rows) return;
@@ -914,8 +916,10 @@ int gemm_tc_split_f32_launch(lh_ctx* ctx, const GemmProblem& p) {
     epi.rope_table = nullptr; epi.rope_cols = 0; epi.rope_dim = 0; epi.rope_seq = 0;
     const int seg_k_blocks = SPLIT_SEGMENT / BK;
     const int64_t ts_a = static_cast<int64_t>(p.M) * ld, ts_b = static_cast<int64_t>(p.N) * ld;
-    rc = bn == 128 ? launch_variant<128, true, 2, true, 4, 3>(ctx, q, epi, seg_k_blocks, ts_a, ts_b)
-                   : launch_variant<64, true, 2, true, 4, 3>(ctx, q, epi, seg_k_blocks, ts_a, ts_b);
+    // (always a programmatic dependent: what precedes it in the stream is this call's own split
+    // kernel or previous segment launch, and its set-up is a third of a 1024^3 product's time)
+    rc = bn == 128 ? launch_variant<128, true, 2, true, 4, 3>(ctx, q, epi, seg_k_blocks, ts_a, ts_b, true)
+                   : launch_variant<64, true, 2, true, 4, 3>(ctx, q, epi, seg_k_blocks, ts_a, ts_b, true);
     if (rc) return rc;
   }
   return LH_OK;

@@ -184,6 +184,37 @@ def test_batched_gemm(ctx):
     assert_parity(host(d), np.einsum("bmk,bkn->bmn", I.to_np(a), I.to_np(b)), "f32")
 
 
+def test_launch_overlap_gives_the_same_bits(ctx):
+    """Programmatic dependent launches (opt-in): a chain of GEMMs each reading its predecessor's
+    result, and an attention call behind them, must give bit for bit what ordinary launches
+    give - every thread waits for the previous kernel before its first global access."""
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(512, 512, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    w = [(torch.randn(512, 512, generator=g) * 0.05).to(torch.bfloat16).cuda() for _ in range(6)]
+    q = torch.randn(1, 4, 512, 128, generator=g).to(torch.bfloat16).cuda()
+
+    def run():
+        a = x
+        for wi in w:
+            d = torch.empty(512, 512, device="cuda", dtype=torch.bfloat16)
+            ctx.gemm(d, a, wi, act=N.ACT_GELU_ERF)
+            a = d
+        kv = a.view(1, 2, 256, 512)[:, :, :, :128].contiguous().expand(1, 2, 256, 128).repeat(1, 2, 2, 1).contiguous()
+        o = torch.empty_like(q)
+        ctx.attention_fwd(o, q, kv, kv, 128**-0.5, True)
+        ctx.sync()
+        return a.clone(), o.clone()
+
+    plain = run()
+    ctx.set_launch_overlap(True)
+    try:
+        for _ in range(3):
+            got = run()
+            assert torch.equal(got[0], plain[0]) and torch.equal(got[1], plain[1])
+    finally:
+        ctx.set_launch_overlap(False)
+
+
 # --------------------------------------------------------------------------------- attention
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("shape", [(1, 1, 1, 128, 128, 128), (1, 2, 1, 256, 256, 128), (2, 4, 2, 384, 384, 128), (1, 2, 2, 200, 333, 64), (2, 3, 3, 77, 77, 64), (1, 4, 1, 130, 514, 128)])
