@@ -253,3 +253,23 @@ def test_sharded_contraction_rounds_per_device_and_agrees_with_the_plain_product
     np.testing.assert_allclose(R.sharded_contraction(a, w, 4, "f32"), a @ w.T, rtol=1e-5, atol=1e-6)
     with pytest.raises(ValueError):
         R.sharded_contraction(a, w, 3, "bf16")
+
+
+def test_depth_and_rounding_count_scale_the_bounds():
+    """One layer keeps the stated bounds; n layers scale them by sqrt(n); a schedule that rounds
+    more often along a layer (the tensor-parallel one) by the square root of that ratio too, and
+    the report says so."""
+    from oracle.check import LAYER_ROUNDINGS, SHARDED_LAYER_ROUNDINGS, parity_report, stack_scale
+
+    assert stack_scale(1) == 1.0 and stack_scale(0) == 1.0
+    assert abs(stack_scale(8) - 8**0.5) < 1e-12
+    assert abs(stack_scale(8, SHARDED_LAYER_ROUNDINGS) - (8 * SHARDED_LAYER_ROUNDINGS / LAYER_ROUNDINGS) ** 0.5) < 1e-12
+    ref = np.linspace(-1.0, 1.0, 4096, dtype=np.float32).reshape(64, 64)
+    out = ref + 0.015  # 1.5 % of max|ref| everywhere, also where ref is 0: outside the one-layer per-element bound (0.7 %), inside the 8-layer one (2 %)
+    one = parity_report(out, ref, "bf16")
+    deep = parity_report(out, ref, "bf16", n_layer=8)
+    sharded = parity_report(out, ref, "bf16", n_layer=8, roundings_per_layer=SHARDED_LAYER_ROUNDINGS)
+    assert not one["ok"] and "tol_rule" not in one
+    assert deep["ok"] and "sqrt(8 layers)" in deep["tol_rule"] and abs(deep["tol"] - 0.0566) < 1e-4
+    assert sharded["ok"] and sharded["tol"] > deep["tol"] and "13" in sharded["tol_rule"]
+    assert sharded["elementwise_excess"] < deep["elementwise_excess"] < one["elementwise_excess"]
